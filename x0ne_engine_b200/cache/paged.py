@@ -153,6 +153,17 @@ class SequenceCache:
     def state(self, entry: int) -> torch.Tensor:
         return self.states[entry]
 
+    def snapshot_states(self, slots: torch.Tensor):
+        """Copies of the fixed-size states of `slots` (a device tensor of slot numbers), to be put back with
+        `restore_states`: for a run whose effect on the sequences is to be undone."""
+        idx = slots.to(torch.int64).clamp(min=0)
+        return idx, [(t, t[idx].clone()) for t in {id(t): t for t in self.states.values()}.values()]
+
+    def restore_states(self, snapshot) -> None:
+        idx, saved = snapshot
+        for t, rows in saved:
+            t[idx] = rows
+
     # ---- slots
     def free_tokens(self) -> int:
         return min((g.pool.available() for g in self.groups if g.need.window is None), default=1 << 40) * self.page_size

@@ -82,7 +82,18 @@ def config_from_folder(folder: str):
         raise ConfigError(f"config.json: {e}") from None
     if not isinstance(d, dict):
         raise ConfigError("config.json: not a JSON object")
-    return config_from_dict(d)
+    config = config_from_dict(d)
+    # A design may leave a size to the shapes of its tensors: such a configuration says so and is completed
+    # from the checkpoint's header (names and shapes only; no tensor is read).
+    if getattr(config, "needs_tensor_shapes", None) is not None and config.needs_tensor_shapes():
+        from ..weights.safetensors_io import open_folder
+        source = open_folder(folder)
+        try:
+            shapes = {name: tuple(source.meta(name).shape) for name in source.names()}
+        finally:
+            source.close()
+        config = config.with_tensor_shapes(shapes)
+    return config
 
 
 def spec_from_folder(folder: str) -> ModelSpec:

@@ -65,10 +65,13 @@ class RunEntry:
     `layer` indexes `ModelSpec.layers`; a layer may be named by several entries (its
     weights are then shared and every entry has a cache of its own).  `reads_cache_of`, if
     set, is the index of an earlier entry of the run order whose cache this entry's mixer
-    reads instead of writing one.
+    reads instead of writing one.  `before`, if set, is a part of the kind "opener" that changes the
+    residual right before this entry's layer runs (what a model adds at the start of a pass over a
+    stretch of layers it repeats).
     """
     layer: int
     reads_cache_of: Optional[int] = None
+    before: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

@@ -18,7 +18,8 @@
 //
 // Beyond that (`AttnExtra`): a chunked mask (the query sees its own chunk of positions only), a
 // value width other than the keys', values read out of the key rows, a per-head sink in the
-// denominator, a per-(row, head) sigmoid gate on the output, and first keys that stay visible
+// denominator, a sigmoid gate on the output (per (row, head), or per value), a per-head slope times the
+// distance i - j taken off every score, and first keys that stay visible
 // whatever the window (they are taken first, in tiles of 32 from key 0, then the window's).  With none of them asked for the
 // operations and their order are the ones above.
 
@@ -39,6 +40,7 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, T* __restrict__ o
     const int kh = head / (q_heads / cache.kv_heads);
     const int pos = row_pos[row], slot = row_slot[row];
     float* qs = smem + w * hd;
+    const float slope = ex.slope != nullptr ? ex.slope[head] : 0.f;
     const T* qr = q + (int64_t)row * (ex.q_ld > 0 ? ex.q_ld : (int64_t)q_heads * hd) + (int64_t)head * hd;
     for (int d = lane; d < hd; d += 32) qs[d] = to_f32(qr[d]) * scale;
     __syncwarp();
@@ -66,7 +68,7 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, T* __restrict__ o
                 const T* kr = base + off;
                 float a = 0.f;
                 for (int d = 0; d < hd; ++d) a = fmaf(qs[d], to_f32(kr[d]), a);
-                s = a;
+                s = ex.slope != nullptr ? a - slope * (float)(pos - j) : a;
             }
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -103,11 +105,12 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, T* __restrict__ o
     }
     T* o = out + ((int64_t)row * q_heads + head) * vd;
     float inv = l > 0.f ? 1.0f / l : 0.f;      // a row with no readable key (a padding row) gets zeros
-    if (ex.gate != nullptr) inv *= 1.0f / (1.0f + expf(-to_f32(((const T*)ex.gate)[(int64_t)row * ex.gate_ld + head])));
+    if (ex.gate != nullptr && ex.gate_wide <= 0) inv *= 1.0f / (1.0f + expf(-to_f32(((const T*)ex.gate)[(int64_t)row * ex.gate_ld + head])));
+    const T* gw = ex.gate != nullptr && ex.gate_wide > 0 ? (const T*)ex.gate + (int64_t)row * ex.gate_ld + (int64_t)head * vd : nullptr;
 #pragma unroll
     for (int i = 0; i < ATT_MAX_I; ++i) {
         const int d = lane + 32 * i;
-        if (d < vd) o[d] = from_f32<T>(acc[i] * inv);
+        if (d < vd) o[d] = from_f32<T>(gw != nullptr ? acc[i] * inv * (1.0f / (1.0f + expf(-to_f32(gw[d])))) : acc[i] * inv);
     }
 }
 

@@ -42,18 +42,21 @@ bool x0ne_pdl_enabled() {
 template <typename T>
 __global__ void add_rmsnorm_any_kernel(float* __restrict__ resid, const T* __restrict__ delta, const T* __restrict__ delta2,
                                        const float* __restrict__ w, T* __restrict__ out,
-                                       const int32_t* __restrict__ rows, int hidden, float eps, int keep) {
+                                       const int32_t* __restrict__ rows, int hidden, float eps, int keep, int ld) {
     extern __shared__ float parked[];
     __shared__ float partial[32];
     pdl_prologue();
+    // blockIdx.y: the group of `hidden` consecutive values of a row of `ld` values that this block norms by itself
     const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
-    float* r = resid + src * hidden;
+    const int64_t at = src * ld + (int64_t)blockIdx.y * hidden;
+    float* r = resid + at;
+    w += (int64_t)blockIdx.y * hidden;
     float sum_sq = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float v = r[i];
         if (delta) {
             // one IEEE add, stored back; two branches of a parallel layer are summed first
-            v = v + (delta2 ? to_f32(delta[src * hidden + i]) + to_f32(delta2[src * hidden + i]) : to_f32(delta[src * hidden + i]));
+            v = v + (delta2 ? to_f32(delta[at + i]) + to_f32(delta2[at + i]) : to_f32(delta[at + i]));
             r[i] = v;
         }
         if (i < keep) parked[i] = v;
@@ -61,7 +64,7 @@ __global__ void add_rmsnorm_any_kernel(float* __restrict__ resid, const T* __res
     }
     const float mean_sq = block_reduce(sum_sq, partial, OpSum(), 0.f) / (float)hidden;
     const float scale = 1.0f / sqrtf(mean_sq + eps);
-    T* o = out + (int64_t)blockIdx.x * hidden;
+    T* o = out + (int64_t)blockIdx.x * ld + (int64_t)blockIdx.y * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         const float v = i < keep ? parked[i] : r[i];     // a thread reads back only what it wrote itself
         o[i] = from_f32<T>(v * scale * w[i]);
@@ -121,7 +124,7 @@ __device__ __forceinline__ void copy2(bf16* d, const bf16* s) { *reinterpret_cas
 template <typename T, int ITS>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, const T* __restrict__ delta2,
                                        const float* __restrict__ w, T* __restrict__ out,
-                                       const int32_t* __restrict__ rows, int hidden, float eps) {
+                                       const int32_t* __restrict__ rows, int hidden, float eps, int ld) {
     __shared__ float sh[32];
     // The weight and the list of rows are older than any kernel still running: they are asked for
     // before the wait for the kernel before this one, so that its end is followed by one trip to
@@ -130,6 +133,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
     constexpr bool EARLY = ITS <= 2;
     pdl_launch_dependents();
     const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
+    const int64_t col0 = (int64_t)blockIdx.y * hidden;      // the group of a row of `ld` values this block norms
+    w += col0;
     float wv[EARLY ? ITS : 1][8];
     if (EARLY) {
 #pragma unroll
@@ -139,10 +144,10 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
         }
     }
     pdl_wait();
-    float* r = resid + src * hidden;
-    const T* d = delta ? delta + src * hidden : nullptr;
-    const T* d2 = delta && delta2 ? delta2 + src * hidden : nullptr;
-    T* o = out + (int64_t)blockIdx.x * hidden;
+    float* r = resid + src * ld + col0;
+    const T* d = delta ? delta + src * ld + col0 : nullptr;
+    const T* d2 = delta && delta2 ? delta2 + src * ld + col0 : nullptr;
+    T* o = out + (int64_t)blockIdx.x * ld + col0;
     float v[ITS][8];
     float ss = 0.f;
 #pragma unroll
@@ -184,31 +189,35 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
 
 template <typename T>
 static void launch_add_rmsnorm_vec(float* resid, const T* delta, const T* delta2, const float* w, T* out, const int32_t* rows, int n_rows,
-                                   int hidden, float eps, int threads, cudaStream_t stream) {
+                                   int hidden, float eps, int threads, int groups, cudaStream_t stream) {
     const int sweeps = (hidden / 8 + threads - 1) / threads;
+    const int ld = hidden * groups;
     if (sweeps <= 1)
-        x0ne_launch(add_rmsnorm_vec_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, stream, resid, delta, delta2, w, out, rows, hidden, eps);
+        x0ne_launch(add_rmsnorm_vec_kernel<T, 1>, dim3(n_rows, groups), dim3(threads), 0, stream, resid, delta, delta2, w, out, rows, hidden, eps, ld);
     else if (sweeps == 2)
-        x0ne_launch(add_rmsnorm_vec_kernel<T, 2>, dim3(n_rows), dim3(threads), 0, stream, resid, delta, delta2, w, out, rows, hidden, eps);
+        x0ne_launch(add_rmsnorm_vec_kernel<T, 2>, dim3(n_rows, groups), dim3(threads), 0, stream, resid, delta, delta2, w, out, rows, hidden, eps, ld);
     else
-        x0ne_launch(add_rmsnorm_vec_kernel<T, VEC_IT>, dim3(n_rows), dim3(threads), 0, stream, resid, delta, delta2, w, out, rows, hidden, eps);
+        x0ne_launch(add_rmsnorm_vec_kernel<T, VEC_IT>, dim3(n_rows, groups), dim3(threads), 0, stream, resid, delta, delta2, w, out, rows, hidden, eps, ld);
 }
 
 // `delta2`, if given with `delta`, is a second branch's result: r = resid + (f32(delta) + f32(delta2)).
-X0NE_API int x0ne_add2_rmsnorm(float* resid, const void* delta, const void* delta2, const float* w, void* out, int dt,
-                               const int32_t* rows, int n_rows, int hidden, float eps, cudaStream_t stream) {
-    X0NE_REQUIRE(n_rows >= 0 && hidden > 0, "add_rmsnorm: rows %d hidden %d", n_rows, hidden);
+// `groups` > 1: a row of `width` values is `groups` equal consecutive parts, each normed by its own root mean
+// square (the weight still has one value per value of the row).
+X0NE_API int x0ne_add2_group_rmsnorm(float* resid, const void* delta, const void* delta2, const float* w, void* out, int dt,
+                                     const int32_t* rows, int n_rows, int width, int groups, float eps, cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && width > 0 && groups >= 1 && groups <= 65535 && width % groups == 0, "add_rmsnorm: rows %d width %d in %d groups", n_rows, width, groups);
     X0NE_REQUIRE(delta != nullptr || delta2 == nullptr, "add_rmsnorm: a second delta without a first");
     if (n_rows == 0) return 0;
+    const int hidden = width / groups;
     if (hidden % 8 == 0 && hidden <= 8 * 1024 * VEC_IT &&
         ((((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)delta2 | (uintptr_t)w | (uintptr_t)out) & 15) == 0)) {
         int threads = (hidden / 8 + 31) / 32 * 32;
         if (threads > 1024) threads = 1024;
         if (hidden / 8 > 512 && hidden / 8 <= 1024) threads = 512;   // two sweeps of 512 rather than one of 1024
         if (dt == X0NE_F32)
-            launch_add_rmsnorm_vec<float>(resid, (const float*)delta, (const float*)delta2, w, (float*)out, rows, n_rows, hidden, eps, threads, stream);
+            launch_add_rmsnorm_vec<float>(resid, (const float*)delta, (const float*)delta2, w, (float*)out, rows, n_rows, hidden, eps, threads, groups, stream);
         else if (dt == X0NE_BF16)
-            launch_add_rmsnorm_vec<bf16>(resid, (const bf16*)delta, (const bf16*)delta2, w, (bf16*)out, rows, n_rows, hidden, eps, threads, stream);
+            launch_add_rmsnorm_vec<bf16>(resid, (const bf16*)delta, (const bf16*)delta2, w, (bf16*)out, rows, n_rows, hidden, eps, threads, groups, stream);
         else
             X0NE_REQUIRE(false, "add_rmsnorm: unknown dtype tag %d", dt);
         X0NE_LAUNCH_CHECK();
@@ -217,12 +226,17 @@ X0NE_API int x0ne_add2_rmsnorm(float* resid, const void* delta, const void* delt
     const int keep = hidden <= 10240 ? hidden : 0;        // up to 40 KB of dynamic shared memory
     const size_t smem = (size_t)keep * sizeof(float);
     if (dt == X0NE_F32)
-        x0ne_launch(add_rmsnorm_any_kernel<float>, dim3(n_rows), dim3(block), smem, stream, resid, (const float*)delta, (const float*)delta2, w, (float*)out, rows, hidden, eps, keep);
+        x0ne_launch(add_rmsnorm_any_kernel<float>, dim3(n_rows, groups), dim3(block), smem, stream, resid, (const float*)delta, (const float*)delta2, w, (float*)out, rows, hidden, eps, keep, width);
     else if (dt == X0NE_BF16)
-        x0ne_launch(add_rmsnorm_any_kernel<bf16>, dim3(n_rows), dim3(block), smem, stream, resid, (const bf16*)delta, (const bf16*)delta2, w, (bf16*)out, rows, hidden, eps, keep);
+        x0ne_launch(add_rmsnorm_any_kernel<bf16>, dim3(n_rows, groups), dim3(block), smem, stream, resid, (const bf16*)delta, (const bf16*)delta2, w, (bf16*)out, rows, hidden, eps, keep, width);
     else
         X0NE_REQUIRE(false, "add_rmsnorm: unknown dtype tag %d", dt);
     X0NE_LAUNCH_CHECK();
+}
+
+X0NE_API int x0ne_add2_rmsnorm(float* resid, const void* delta, const void* delta2, const float* w, void* out, int dt,
+                               const int32_t* rows, int n_rows, int hidden, float eps, cudaStream_t stream) {
+    return x0ne_add2_group_rmsnorm(resid, delta, delta2, w, out, dt, rows, n_rows, hidden, 1, eps, stream);
 }
 
 X0NE_API int x0ne_add_rmsnorm(float* resid, const void* delta, const float* w, void* out, int dt,
@@ -786,3 +800,42 @@ X0NE_API int x0ne_embedding(const void* table, int dt, const int32_t* tokens, fl
     X0NE_LAUNCH_CHECK();
 }
 
+
+// ----------------------------------------------------------------------------------------
+// The start of a pass over a run of layers that a model repeats:
+//   resid[r] = ((resid[r] + delta[r]) + scale * table[token[r]]) + step[c]
+// in float32, one IEEE add after the other.  `delta` (the pending result of the layer before) and the
+// embedding term (`table` null: not added) are optional; `step` is one vector of the pass.
+// ----------------------------------------------------------------------------------------
+template <typename T, typename E>
+__global__ void open_pass_kernel(float* __restrict__ resid, const T* __restrict__ delta, const E* __restrict__ table,
+                                 const int32_t* __restrict__ tokens, float scale, const float* __restrict__ step, int hidden, int vocab) {
+    pdl_prologue();
+    const int row = blockIdx.x;
+    float* r = resid + (int64_t)row * hidden;
+    const int t = table != nullptr ? tokens[row] : -1;
+    const E* e = (table != nullptr && t >= 0 && t < vocab) ? table + (int64_t)t * hidden : nullptr;
+    const T* d = delta != nullptr ? delta + (int64_t)row * hidden : nullptr;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = r[i];
+        if (d != nullptr) v = v + to_f32(d[i]);
+        if (e != nullptr) v = v + to_f32(e[i]) * scale;
+        if (step != nullptr) v = v + step[i];
+        r[i] = v;
+    }
+}
+
+X0NE_API int x0ne_open_pass(float* resid, const void* delta, int dt, const void* table, int table_dt, const int32_t* tokens, float scale,
+                            const float* step, int n_rows, int hidden, int vocab, cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && hidden > 0 && (table == nullptr || (tokens != nullptr && vocab > 0)), "open_pass: rows %d hidden %d", n_rows, hidden);
+    X0NE_REQUIRE((dt == X0NE_F32 || dt == X0NE_BF16) && (table_dt == X0NE_F32 || table_dt == X0NE_BF16), "open_pass: unknown dtype tag");
+    if (n_rows == 0) return 0;
+    const int block = hidden >= 256 ? 256 : (hidden + 31) / 32 * 32;
+#define X0NE_OPEN(T, E) x0ne_launch(open_pass_kernel<T, E>, dim3(n_rows), dim3(block), 0, stream, resid, (const T*)delta, (const E*)table, tokens, scale, step, hidden, vocab)
+    if (dt == X0NE_F32 && table_dt == X0NE_F32) X0NE_OPEN(float, float);
+    else if (dt == X0NE_F32) X0NE_OPEN(float, bf16);
+    else if (table_dt == X0NE_F32) X0NE_OPEN(bf16, float);
+    else X0NE_OPEN(bf16, bf16);
+#undef X0NE_OPEN
+    X0NE_LAUNCH_CHECK();
+}

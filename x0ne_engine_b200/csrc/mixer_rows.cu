@@ -624,3 +624,121 @@ X0NE_API int x0ne_relu2(const void* x, void* out, int dt, int64_t total, cudaStr
     else x0ne_launch(relu2_kernel<bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)x, (bf16*)out, total);
     X0NE_LAUNCH_CHECK();
 }
+
+// ----------------------------------------------------------------------------------------
+// Per-head preparation of an attention without rotation.  src holds, per row, the queries at column 0,
+// the keys at k_col and the values at v_col (one packed projection; more columns may follow).
+//   query head:  x / sqrt(mean(x^2) + eps) * norm_q[d] * temperature(pos)      -> q_out [rows][q_heads * head_dim]
+//                temperature(p) = 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)   (temp_every <= 0: 1)
+//   key head:    x / sqrt(mean(x^2) + eps) * norm_k[d]                          -> the row's place in the pages
+//   value head:  x / sqrt(mean(x^2) + eps) (v_unit) or x as it is               -> the row's place in the pages
+// norm_q / norm_k hold head_dim values shared by all heads (null: no weight).  One warp per (row, head of q, k or v);
+// sums of squares, the logarithm and the products are float32.  Rows without a page write no keys or values.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void head_norm_kv_write_kernel(const T* __restrict__ src, int ld, int k_col, int v_col, const float* __restrict__ norm_q,
+                                          const float* __restrict__ norm_k, float eps, float temp_coef, int temp_every, int v_unit,
+                                          T* __restrict__ q_out, int q_heads, PagedCache cache, const int32_t* __restrict__ row_slot,
+                                          const int32_t* __restrict__ row_pos, int n_rows) {
+    pdl_prologue();
+    const int lane = threadIdx.x & 31;
+    const int units = q_heads + 2 * cache.kv_heads;
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (int64_t)n_rows * units) return;
+    const int row = (int)(item / units), unit = (int)(item % units);
+    const int hd = cache.head_dim, vd = cache_v_dim(cache);
+    const int pos = row_pos[row];
+    const T* x;
+    T* dst;
+    const float* w = nullptr;
+    int n;
+    float mul = 1.f;
+    bool normed = true;
+    if (unit < q_heads) {
+        x = src + (int64_t)row * ld + (int64_t)unit * hd;
+        dst = q_out + ((int64_t)row * q_heads + unit) * hd;
+        w = norm_q;
+        n = hd;
+        if (temp_every > 0) mul = 1.0f + temp_coef * logf((float)((pos + 1) / temp_every + 1));
+    } else {
+        const bool is_k = unit < q_heads + cache.kv_heads;
+        const int kh = unit - q_heads - (is_k ? 0 : cache.kv_heads);
+        const int64_t off = cache_row_offset(cache, row_slot[row], pos, kh, is_k ? 0 : 1);
+        if (off < 0) return;
+        n = is_k ? hd : vd;
+        x = src + (int64_t)row * ld + (is_k ? k_col : v_col) + (int64_t)kh * n;
+        dst = (T*)cache.base + off;
+        w = is_k ? norm_k : nullptr;
+        normed = is_k || v_unit != 0;
+    }
+    float scale = mul;
+    if (normed) {
+        float ss = 0.f;
+        for (int i = lane; i < n; i += 32) {
+            const float v = to_f32(x[i]);
+            ss = fmaf(v, v, ss);
+        }
+        ss = warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / (float)n + eps);
+    }
+    for (int i = lane; i < n; i += 32) {
+        float v = to_f32(x[i]) * scale;
+        if (w != nullptr) v *= w[i];
+        if (normed && mul != 1.f) v *= mul;
+        dst[i] = from_f32<T>(v);
+    }
+}
+
+X0NE_API int x0ne_head_norm_kv_write(const void* src, int dt, int ld, int k_col, int v_col, const float* norm_q, const float* norm_k,
+                                     float eps, float temp_coef, int temp_every, int v_unit, void* q_out, int q_heads,
+                                     PagedCache cache, const int32_t* row_slot, const int32_t* row_pos, int n_rows,
+                                     cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && q_heads > 0 && cache.kv_heads > 0 && cache.head_dim > 0 && cache.v_dim >= 0, "head_norm: bad sizes");
+    const int vd = cache_v_dim(cache);
+    X0NE_REQUIRE(k_col >= q_heads * cache.head_dim && v_col >= k_col + cache.kv_heads * cache.head_dim && ld >= v_col + cache.kv_heads * vd,
+                 "head_norm: columns %d, %d do not fit rows of %d", k_col, v_col, ld);
+    if (n_rows == 0) return 0;
+    const int warps = 4;
+    const int64_t items = (int64_t)n_rows * (q_heads + 2 * cache.kv_heads);
+    X0NE_REQUIRE((items + warps - 1) / warps <= 0x7fffffff, "head_norm: too many rows");
+    const dim3 grid((unsigned)((items + warps - 1) / warps));
+    if (dt == X0NE_F32)
+        x0ne_launch(head_norm_kv_write_kernel<float>, grid, dim3(warps * 32), 0, stream, (const float*)src, ld, k_col, v_col, norm_q, norm_k,
+                    eps, temp_coef, temp_every, v_unit, (float*)q_out, q_heads, cache, row_slot, row_pos, n_rows);
+    else if (dt == X0NE_BF16)
+        x0ne_launch(head_norm_kv_write_kernel<bf16>, grid, dim3(warps * 32), 0, stream, (const bf16*)src, ld, k_col, v_col, norm_q, norm_k,
+                    eps, temp_coef, temp_every, v_unit, (bf16*)q_out, q_heads, cache, row_slot, row_pos, n_rows);
+    else
+        X0NE_REQUIRE(false, "head_norm: unknown dtype tag %d", dt);
+    X0NE_LAUNCH_CHECK();
+}
+
+// ----------------------------------------------------------------------------------------
+// Bias and activation of a product's rows: out = act(x + bias), float32 inside.
+//   act 0: none
+//   act 1: a unit with a quadratic positive and an exponential negative branch and the slope 1/2 at zero,
+//          z > 0: a z^2 + z / 2;  z <= 0: b (exp(z) - 1 - z) + z / 2      (a, b >= 0 given by the caller)
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void bias_act_kernel(const T* __restrict__ x, const float* __restrict__ bias, T* __restrict__ out, int width, int64_t total,
+                                int act, float a, float b) {
+    pdl_prologue();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        float z = to_f32(x[i]);
+        if (bias != nullptr) z += bias[i % width];
+        if (act == 1) z = z > 0.f ? fmaf(a * z, z, 0.5f * z) : fmaf(b, expm1f(z) - z, 0.5f * z);
+        out[i] = from_f32<T>(z);
+    }
+}
+
+X0NE_API int x0ne_bias_act(const void* x, const float* bias, void* out, int dt, int n_rows, int width, int act, float a, float b,
+                           cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && width > 0 && (act == 0 || act == 1) && (dt == X0NE_F32 || dt == X0NE_BF16),
+                 "bias_act: rows %d width %d act %d dtype tag %d", n_rows, width, act, dt);
+    if (n_rows == 0) return 0;
+    const int64_t total = (int64_t)n_rows * width;
+    const unsigned grid = (unsigned)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
+    if (dt == X0NE_F32) x0ne_launch(bias_act_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)x, bias, (float*)out, width, total, act, a, b);
+    else x0ne_launch(bias_act_kernel<bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)x, bias, (bf16*)out, width, total, act, a, b);
+    X0NE_LAUNCH_CHECK();
+}

@@ -6,6 +6,8 @@
 //            its largest c, only the `keep` best groups stay (the others' c count as minus infinity);
 //            the `top` largest c are chosen (equal values: the lower index first)
 //   weights  the chosen outputs' s, as they are
+// or, for a router that chooses on its logits (`on_logits`): s = z + correction (a bias of the router) without a
+// softmax, the `top` largest s are chosen, and the weights are the softmax over the chosen s alone.
 // The last `n - experts` router outputs are identity experts: their output is the row itself, they
 // have no weights and form no group of pairs.
 //
@@ -28,7 +30,7 @@
 // ----------------------------------------------------------------------------------------
 __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ correction, int n, int groups,
                                  int keep, int top, int n_rows, int32_t* __restrict__ chosen, float* __restrict__ weights,
-                                 float* __restrict__ sgate, int sg_col) {
+                                 float* __restrict__ sgate, int sg_col, int on_logits) {
     extern __shared__ float rt_smem[];
     pdl_prologue();
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -38,19 +40,26 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, const flo
     float* c = s + n;                                       // choice values
     float* gv = c + n;                                      // group values
     const float* zr = z + (int64_t)row * ldz;
-    float m = -INFINITY;
-    for (int i = lane; i < n; i += 32) m = fmaxf(m, zr[i]);
-    m = warp_max(m);
-    float sum = 0.f;
-    for (int i = lane; i < n; i += 32) {
-        const float e = expf(zr[i] - m);
-        s[i] = e;
-        sum += e;
-    }
-    sum = warp_sum(sum);
-    for (int i = lane; i < n; i += 32) {
-        s[i] = s[i] / sum;
-        c[i] = s[i] + correction[i];
+    if (on_logits) {
+        for (int i = lane; i < n; i += 32) {
+            s[i] = zr[i] + correction[i];
+            c[i] = s[i];
+        }
+    } else {
+        float m = -INFINITY;
+        for (int i = lane; i < n; i += 32) m = fmaxf(m, zr[i]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int i = lane; i < n; i += 32) {
+            const float e = expf(zr[i] - m);
+            s[i] = e;
+            sum += e;
+        }
+        sum = warp_sum(sum);
+        for (int i = lane; i < n; i += 32) {
+            s[i] = s[i] / sum;
+            c[i] = s[i] + correction[i];
+        }
     }
     __syncwarp();
     const int per = n / groups;
@@ -101,6 +110,16 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, const flo
             c[bi] = INFINITY;                // taken
         }
         __syncwarp();
+    }
+    if (on_logits && lane == 0) {       // softmax over the chosen values, in the order they were chosen (the first is the largest)
+        float* wr = weights + (int64_t)row * top;
+        const float m = wr[0];
+        float sum = 0.f;
+        for (int r = 0; r < top; ++r) {
+            wr[r] = expf(wr[r] - m);
+            sum += wr[r];
+        }
+        for (int r = 0; r < top; ++r) wr[r] = wr[r] / sum;
     }
     if (sgate != nullptr && lane == 0) sgate[row] = 1.0f / (1.0f + expf(-zr[sg_col]));
 }
@@ -162,17 +181,21 @@ __global__ void moe_group_kernel(const int32_t* __restrict__ chosen, int pairs, 
 // ----------------------------------------------------------------------------------------
 // The experts' products over the tiles, on the CUDA cores: one fused multiply-add chain per output
 // over k ascending (the 32-bit path; also the path of shapes the tensor-core kernel does not take).
-//   UP:   act[pair][n] = relu(sum_k x[pair / top][k] w[e][n][k])^2             (activation type)
-//   DOWN: y[pair][n]   = sum_k act[pair][k] w[e][n][k]                          (float32)
+//   ACT 1 (up):       act[pair][n] = relu(sum_k x[pair / top][k] w[e][n][k])^2             (activation type)
+//   ACT 2 (gated up): act[pair][n] = silu(sum_k x[..][k] w[e][n][k]) * sum_k x[..][k] w[e][N + n][k]
+//                     (an expert's weight holds its N gate rows, then its N up rows)
+//   ACT 0 (down):     y[pair][n]   = sum_k act[pair][k] w[e][n][k]                          (float32)
 // Tile 32 pairs x 64 outputs x 16 k, 256 threads, 2 x 4 outputs per thread.
 // ----------------------------------------------------------------------------------------
-template <typename T, bool UP>
+template <typename T, int ACT>
 __global__ void __launch_bounds__(256) moe_product_kernel(const T* __restrict__ a, int64_t lda, const T* __restrict__ w, int N, int K,
                                                           const int32_t* __restrict__ listed, const int32_t* __restrict__ tiles,
                                                           int top, void* __restrict__ out) {
     __shared__ float As[16][MOE_TILE_M + 4];
     __shared__ float Ws[16][64 + 4];
+    __shared__ float Us[ACT == 2 ? 16 : 1][64 + 4];
     __shared__ int pair_s[MOE_TILE_M];
+    constexpr bool UP = ACT != 0;
     pdl_prologue();
     const int tile = blockIdx.y;
     const int count = tiles[3 * tile + 2];
@@ -181,9 +204,10 @@ __global__ void __launch_bounds__(256) moe_product_kernel(const T* __restrict__ 
     const int tid = threadIdx.x, n0 = blockIdx.x * 64;
     if (tid < MOE_TILE_M) pair_s[tid] = tid < count ? listed[first + tid] : -1;
     __syncthreads();
-    const T* we = w + (int64_t)e * N * K;
+    const T* we = w + (int64_t)e * (ACT == 2 ? 2 : 1) * N * K;
     const int tx = tid % 16, ty = tid / 16;
     float acc[2][4] = {};
+    float acu[ACT == 2 ? 2 : 1][4] = {};
     for (int k0 = 0; k0 < K; k0 += 16) {
 #pragma unroll
         for (int it = 0; it < 2; ++it) {
@@ -198,6 +222,7 @@ __global__ void __launch_bounds__(256) moe_product_kernel(const T* __restrict__ 
             const int r = idx / 16, kk = idx % 16;
             const int gn = n0 + r, gk = k0 + kk;
             Ws[kk][r] = (gn < N && gk < K) ? to_f32(we[(int64_t)gn * K + gk]) : 0.f;
+            if (ACT == 2) Us[kk][r] = (gn < N && gk < K) ? to_f32(we[(int64_t)(N + gn) * K + gk]) : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -211,6 +236,12 @@ __global__ void __launch_bounds__(256) moe_product_kernel(const T* __restrict__ 
             for (int i = 0; i < 2; ++i)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+            if (ACT == 2) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acu[i][j] = fmaf(av[i], Us[kk][tx * 4 + j], acu[i][j]);
+            }
         }
         __syncthreads();
     }
@@ -222,7 +253,10 @@ __global__ void __launch_bounds__(256) moe_product_kernel(const T* __restrict__ 
         for (int j = 0; j < 4; ++j) {
             const int gn = n0 + tx * 4 + j;
             if (gn >= N) continue;
-            if (UP) {
+            if (ACT == 2) {
+                const float g = acc[i][j];
+                ((T*)out)[(int64_t)p * N + gn] = from_f32<T>(g / (1.0f + expf(-g)) * acu[i][j]);
+            } else if (UP) {
                 const float r = fmaxf(acc[i][j], 0.f);
                 ((T*)out)[(int64_t)p * N + gn] = from_f32<T>(r * r);
             } else {
@@ -325,7 +359,7 @@ X0NE_API int x0ne_moe_max_tiles(int pairs, int experts, int tile_m) {
 }
 
 X0NE_API int x0ne_moe_route(const float* z, int ldz, const float* correction, int n, int groups, int keep, int top, int n_rows,
-                            int32_t* chosen, float* weights, float* sgate, int sg_col, cudaStream_t stream) {
+                            int32_t* chosen, float* weights, float* sgate, int sg_col, int on_logits, cudaStream_t stream) {
     X0NE_REQUIRE(n_rows >= 0 && n > 0 && ldz >= n && top > 0 && top <= n, "moe_route: rows %d outputs %d ld %d top %d", n_rows, n, ldz, top);
     X0NE_REQUIRE(groups >= 1 && n % groups == 0 && keep >= 1 && keep <= groups && top <= keep * (n / groups),
                  "moe_route: %d outputs in %d groups of which %d stay cannot give %d choices", n, groups, keep, top);
@@ -335,7 +369,7 @@ X0NE_API int x0ne_moe_route(const float* z, int ldz, const float* correction, in
     const size_t smem = (size_t)warps * (2 * n + groups) * sizeof(float);
     X0NE_REQUIRE(smem <= 48 * 1024, "moe_route: %d router outputs are more than the kernel holds", n);
     x0ne_launch(moe_route_kernel, dim3((n_rows + warps - 1) / warps), dim3(warps * 32), smem, stream, z, ldz, correction, n, groups, keep,
-                top, n_rows, chosen, weights, sgate, sg_col);
+                top, n_rows, chosen, weights, sgate, sg_col, on_logits);
     X0NE_LAUNCH_CHECK();
 }
 
@@ -353,19 +387,22 @@ X0NE_API int x0ne_moe_group(const int32_t* chosen, int pairs, int experts, int32
 
 // which = 0: up product with the squared ReLU (a: the rows [*, K], out: activation type [pairs][N]);
 // which = 1: down product (a: the activations [pairs][K], out: float32 [pairs][N]).  w: [experts][N][K].
+// which = 2: gated up product, silu(gate) * up (w: [experts][2 N][K], an expert's gate rows before its up rows).
 X0NE_API int x0ne_moe_product(int which, const void* a, int64_t lda, const void* w, int dt, int N, int K, const int32_t* listed,
                               const int32_t* tiles, int max_tiles, int top, void* out, cudaStream_t stream) {
-    X0NE_REQUIRE((which == 0 || which == 1) && N > 0 && K > 0 && lda >= K && top > 0 && max_tiles >= 0, "moe_product: N %d K %d lda %lld", N, K, (long long)lda);
+    X0NE_REQUIRE((which == 0 || which == 1 || which == 2) && N > 0 && K > 0 && lda >= K && top > 0 && max_tiles >= 0, "moe_product: N %d K %d lda %lld", N, K, (long long)lda);
     X0NE_REQUIRE(dt == X0NE_F32 || dt == X0NE_BF16, "moe_product: unknown dtype tag %d", dt);
     if (max_tiles == 0) return 0;
     X0NE_REQUIRE(max_tiles <= 65535, "moe_product: %d tiles in one launch", max_tiles);
     const dim3 grid((N + 63) / 64, max_tiles), block(256);
     if (dt == X0NE_F32) {
-        if (which == 0) x0ne_launch(moe_product_kernel<float, true>, grid, block, 0, stream, (const float*)a, lda, (const float*)w, N, K, listed, tiles, top, out);
-        else x0ne_launch(moe_product_kernel<float, false>, grid, block, 0, stream, (const float*)a, lda, (const float*)w, N, K, listed, tiles, top, out);
+        if (which == 0) x0ne_launch(moe_product_kernel<float, 1>, grid, block, 0, stream, (const float*)a, lda, (const float*)w, N, K, listed, tiles, top, out);
+        else if (which == 2) x0ne_launch(moe_product_kernel<float, 2>, grid, block, 0, stream, (const float*)a, lda, (const float*)w, N, K, listed, tiles, top, out);
+        else x0ne_launch(moe_product_kernel<float, 0>, grid, block, 0, stream, (const float*)a, lda, (const float*)w, N, K, listed, tiles, top, out);
     } else {
-        if (which == 0) x0ne_launch(moe_product_kernel<bf16, true>, grid, block, 0, stream, (const bf16*)a, lda, (const bf16*)w, N, K, listed, tiles, top, out);
-        else x0ne_launch(moe_product_kernel<bf16, false>, grid, block, 0, stream, (const bf16*)a, lda, (const bf16*)w, N, K, listed, tiles, top, out);
+        if (which == 0) x0ne_launch(moe_product_kernel<bf16, 1>, grid, block, 0, stream, (const bf16*)a, lda, (const bf16*)w, N, K, listed, tiles, top, out);
+        else if (which == 2) x0ne_launch(moe_product_kernel<bf16, 2>, grid, block, 0, stream, (const bf16*)a, lda, (const bf16*)w, N, K, listed, tiles, top, out);
+        else x0ne_launch(moe_product_kernel<bf16, 0>, grid, block, 0, stream, (const bf16*)a, lda, (const bf16*)w, N, K, listed, tiles, top, out);
     }
     X0NE_LAUNCH_CHECK();
 }

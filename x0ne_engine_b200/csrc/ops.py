@@ -47,16 +47,22 @@ class AttnExtraArg(Structure):
     """Mirror of `struct AttnExtra` in common.cuh: what an attention kernel is asked for beyond causal
     softmax over a window (all zero: nothing)."""
     _fields_ = [("chunk", c_int32), ("v_from_k", c_int32), ("sink", c_void_p), ("gate", c_void_p),
-                ("gate_ld", c_int64), ("q_ld", c_int64), ("keep_first", c_int32)]
+                ("gate_ld", c_int64), ("q_ld", c_int64), ("keep_first", c_int32), ("gate_wide", c_int32), ("slope", c_void_p)]
 
 
 def attn_extra(chunk: int = 0, v_from_k: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-               gate_ld: int = 0, q_ld: int = 0, keep_first: int = 0) -> AttnExtraArg:
-    """`sink`: float32 per q head.  `gate`: a view whose element (row, head) lies at row * gate_ld + head.
-    `keep_first`: the keys at positions below it stay visible to every later query, whatever the window or chunk."""
+               gate_ld: int = 0, q_ld: int = 0, keep_first: int = 0, gate_wide: bool = False,
+               slope: Optional[torch.Tensor] = None) -> AttnExtraArg:
+    """`sink`: float32 per q head.  `gate`: a view whose element (row, head) lies at row * gate_ld + head; with
+    `gate_wide` it holds a value per (row, head, value) at row * gate_ld + head * value width + value.
+    `keep_first`: the keys at positions below it stay visible to every later query, whatever the window or chunk.
+    `slope`: float32 per q head; slope[h] * (i - j) is taken off the scaled score of query i and key j."""
     if sink is not None:
         _need(sink, torch.float32, "sink")
-    return AttnExtraArg(int(chunk or 0), int(v_from_k or 0), _ptr(sink), _ptr(gate), int(gate_ld), int(q_ld), int(keep_first or 0))
+    if slope is not None:
+        _need(slope, torch.float32, "distance slopes")
+    return AttnExtraArg(int(chunk or 0), int(v_from_k or 0), _ptr(sink), _ptr(gate), int(gate_ld), int(q_ld), int(keep_first or 0),
+                        1 if gate_wide else 0, _ptr(slope))
 
 
 class SampleIOArg(Structure):
@@ -79,7 +85,15 @@ _SIGNATURES = {
     "x0ne_add_normed_rmsnorm": [_P, _P, _P, _F, _P, _P, _I, _P, _I, _I, _F, _P],
     "x0ne_whole_norm_rope_kv_write": [_P, _I, _I, _I, _I, _P, _P, _F, _P, _I, _P, _I, _P, _I, None, _P, _P, _I, _I, _P],
     "x0ne_relu2": [_P, _P, _I, _L, _P],
-    "x0ne_moe_route": [_P, _I, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P],
+    "x0ne_moe_route": [_P, _I, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P],
+    "x0ne_add2_group_rmsnorm": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _P],
+    "x0ne_open_pass": [_P, _P, _I, _P, _I, _P, _F, _P, _I, _I, _I, _P],
+    "x0ne_head_norm_kv_write": [_P, _I, _I, _I, _I, _P, _P, _F, _F, _I, _I, _P, _I, None, _P, _P, _I, _P],
+    "x0ne_bias_act": [_P, _P, _P, _I, _I, _I, _I, _F, _F, _P],
+    "x0ne_token_shift_mix": [_P, _I, _P, _I, _P, _L, _P, _L, _L, _P, _P, _I, _I, _P],
+    "x0ne_wkv_scan": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _P],
+    "x0ne_head_norm_gate": [_P, _P, _P, _P, _I, _I, _I, _I, _F, _P],
+    "x0ne_tanh_rows": [_P, _P, _I, _L, _P],
     "x0ne_moe_group": [_P, _I, _I, _P, _P, _P, _I, _I, _P, _P],
     "x0ne_moe_gather_rows": [_P, _I, _P, _P, _I, _I, _P, _I, _P],
     "x0ne_moe_product_tc": [_I, _P, _L, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P],
@@ -199,10 +213,10 @@ def embedding(table: torch.Tensor, tokens: torch.Tensor, resid: torch.Tensor, n_
 
 
 def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, out: torch.Tensor,
-                n_rows: int, eps: float, rows: Optional[torch.Tensor] = None) -> None:
+                n_rows: int, eps: float, rows: Optional[torch.Tensor] = None, groups: int = 1) -> None:
     """resid += delta (if given); out = rmsnorm(resid) * weight.  `rows` gathers source rows.  `delta` may
     be a pair of tensors, the results of two branches that read the same normed rows: their float32
-    sum is added."""
+    sum is added.  `groups` > 1: a row is that many equal consecutive parts, each normed by its own root mean square."""
     lib = _lib("core")
     delta2 = None
     if isinstance(delta, (tuple, list)):
@@ -231,6 +245,13 @@ def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, out: torch.Ten
         _need(delta2, out.dtype, "second delta")
         if delta2.shape[-1] != hidden:
             raise KernelError("add_rmsnorm: delta width differs from the norm's")
+    if groups != 1:
+        if groups < 1 or hidden % groups:
+            raise KernelError(f"add_rmsnorm: rows of {hidden} values do not split into {groups} equal parts")
+        _check(lib, lib.x0ne_add2_group_rmsnorm(_ptr(resid), _ptr(delta), _ptr(delta2), _ptr(weight), _ptr(out), dtype_tag(out.dtype),
+                                                _ptr(rows), n_rows, hidden, groups, eps, _stream()), "add_rmsnorm")
+        return
+    if delta2 is not None:
         _check(lib, lib.x0ne_add2_rmsnorm(_ptr(resid), _ptr(delta), _ptr(delta2), _ptr(weight), _ptr(out), dtype_tag(out.dtype),
                                           _ptr(rows), n_rows, hidden, eps, _stream()), "add_rmsnorm")
         return
@@ -333,9 +354,11 @@ def moe_tc_takes(dtype: torch.dtype, pairs: int, *widths: int) -> bool:
 
 
 def moe_route(z: torch.Tensor, correction: torch.Tensor, n: int, groups: int, keep: int, top: int, n_rows: int,
-              chosen: torch.Tensor, weights: torch.Tensor, sgate: Optional[torch.Tensor] = None, sg_col: int = 0) -> None:
+              chosen: torch.Tensor, weights: torch.Tensor, sgate: Optional[torch.Tensor] = None, sg_col: int = 0,
+              on_logits: bool = False) -> None:
     """The router's choice per row from float32 logits z [rows, >= n] (see moe.cu): `chosen` int32 [rows, top],
-    `weights` float32 [rows, top]; `sgate` float32 [rows] = sigmoid(z[:, sg_col])."""
+    `weights` float32 [rows, top]; `sgate` float32 [rows] = sigmoid(z[:, sg_col]).  `on_logits`: the choice is made on
+    z + correction itself (no softmax over all outputs) and the weights are the softmax over the chosen values."""
     lib = _lib("core")
     _need(z, torch.float32, "router logits")
     _need(correction, torch.float32, "router correction")
@@ -347,7 +370,7 @@ def moe_route(z: torch.Tensor, correction: torch.Tensor, n: int, groups: int, ke
             or (sgate is not None and sgate.numel() < n_rows):
         raise KernelError("moe_route: buffers do not match the rows and choices asked for")
     _check(lib, lib.x0ne_moe_route(_ptr(z), z.shape[-1], _ptr(correction), n, groups, keep, top, n_rows, _ptr(chosen),
-                                   _ptr(weights), _ptr(sgate), sg_col, _stream()), "moe_route")
+                                   _ptr(weights), _ptr(sgate), sg_col, 1 if on_logits else 0, _stream()), "moe_route")
 
 
 def moe_group(chosen: torch.Tensor, pairs: int, experts: int, offsets: torch.Tensor, listed: torch.Tensor,
@@ -397,15 +420,16 @@ def moe_product_tc(which: int, a: torch.Tensor, w: torch.Tensor, listed: torch.T
 def moe_product(which: int, a: torch.Tensor, w: torch.Tensor, listed: torch.Tensor, tiles: torch.Tensor, n_tiles: int, top: int,
                 out: torch.Tensor) -> None:
     """The experts' products over the first n_tiles tiles.  which 0: out[pair] = relu(x[pair // top] W_e^T)^2 in the
-    activation type; which 1: out[pair] = act[pair] W_e^T in float32.  w is [experts, N, K]."""
+    activation type; which 1: out[pair] = act[pair] W_e^T in float32.  w is [experts, N, K].  which 2: out[pair] =
+    silu(x W_gate_e^T) * (x W_up_e^T) with w [experts, 2 N, K], an expert's gate rows before its up rows."""
     _need(a, w.dtype, "expert input")
     _need(w, w.dtype, "expert weights")
     _need(out, torch.float32 if which == 1 else w.dtype, "expert output")
     _need(listed, torch.int32, "listed pairs")
     _need(tiles, torch.int32, "tile table")
-    if w.dim() != 3 or a.shape[-1] != w.shape[2] or out.shape[-1] != w.shape[1] or tiles.numel() < 3 * n_tiles:
+    n, k = (w.shape[1] // 2 if which == 2 else w.shape[1]), w.shape[2]
+    if w.dim() != 3 or a.shape[-1] != k or out.shape[-1] != n or tiles.numel() < 3 * n_tiles or (which == 2 and w.shape[1] % 2):
         raise KernelError("moe_product: shapes do not match")
-    n, k = w.shape[1], w.shape[2]
     lib = _lib("core")
     _check(lib, lib.x0ne_moe_product(which, _ptr(a), a.shape[-1], _ptr(w), dtype_tag(w.dtype), n, k, _ptr(listed), _ptr(tiles),
                                      n_tiles, top, _ptr(out), _stream()), "moe_product")
@@ -1035,3 +1059,135 @@ def attention_prefill_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: PagedCa
             tile_row0.data_ptr() + 4 * first, n, _ptr(seq_first_row), _ptr(seq_slot), _ptr(seq_pos0),
             q_heads, scale, window, _ptr(gemm_tc_status(q.device)), _stream()),
             "attention_prefill_tcgen05")
+
+
+# ---------------------------------------------------------------------------------------------
+# pass opener, per-head attention preparation without rotation, bias + activation (module `core`)
+# ---------------------------------------------------------------------------------------------
+def open_pass(resid: torch.Tensor, delta: Optional[torch.Tensor], table: Optional[torch.Tensor], tokens: Optional[torch.Tensor],
+              scale: float, step: Optional[torch.Tensor], n_rows: int) -> None:
+    """resid = ((resid + delta) + scale * table[tokens]) + step in float32; each term is optional."""
+    lib = _lib("core")
+    _need(resid, torch.float32, "residual")
+    hidden = resid.shape[-1]
+    if delta is not None:
+        _need(delta, delta.dtype, "delta")
+    if step is not None:
+        _need(step, torch.float32, "step vector")
+    if table is not None:
+        _need(tokens, torch.int32, "tokens")
+        _need(table, table.dtype, "embedding table")
+    if resid.numel() < n_rows * hidden or (delta is not None and (delta.shape[-1] != hidden or delta.numel() < n_rows * hidden)) \
+            or (step is not None and step.numel() != hidden) or (table is not None and (table.shape[-1] != hidden or tokens.numel() < n_rows)):
+        raise KernelError("open_pass: widths or rows do not match")
+    _check(lib, lib.x0ne_open_pass(_ptr(resid), _ptr(delta), dtype_tag(delta.dtype) if delta is not None else F32, _ptr(table),
+                                   dtype_tag(table.dtype) if table is not None else F32, _ptr(tokens), float(scale), _ptr(step),
+                                   n_rows, hidden, table.shape[0] if table is not None else 0, _stream()), "open_pass")
+
+
+def head_norm_kv_write(src: torch.Tensor, k_col: int, v_col: int, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
+                       eps: float, temp_coef: float, temp_every: int, v_unit: bool, q_out: torch.Tensor, q_heads: int,
+                       cache: PagedCacheArg, row_slot: torch.Tensor, row_pos: torch.Tensor, n_rows: int) -> None:
+    """Per-head RMS norm of the queries (columns from 0) and keys (from k_col) of `src` with one weight of head_dim
+    values each, the queries times 1 + temp_coef ln(floor((pos + 1) / temp_every) + 1) (temp_every 0: no such factor),
+    the values (from v_col) brought to unit root mean square if `v_unit`; queries to q_out, keys and values to the pages."""
+    lib = _lib("core")
+    _need(src, src.dtype, "projection")
+    _need(q_out, src.dtype, "queries")
+    for t, what in ((q_norm, "query norm weight"), (k_norm, "key norm weight")):
+        if t is not None:
+            _need(t, torch.float32, what)
+            if t.numel() != cache.head_dim:
+                raise KernelError(f"head_norm_kv_write: the {what} does not have head_dim values")
+    if src.numel() < n_rows * src.shape[-1] or q_out.shape[-1] != q_heads * cache.head_dim or q_out.numel() < n_rows * q_out.shape[-1]:
+        raise KernelError("head_norm_kv_write: buffers smaller than the rows asked for")
+    _check(lib, lib.x0ne_head_norm_kv_write(_ptr(src), dtype_tag(src.dtype), src.shape[-1], k_col, v_col, _ptr(q_norm), _ptr(k_norm),
+                                            float(eps), float(temp_coef), int(temp_every or 0), 1 if v_unit else 0, _ptr(q_out), q_heads,
+                                            cache, _ptr(row_slot), _ptr(row_pos), n_rows, _stream()), "head_norm_kv_write")
+
+
+ACT_NONE, ACT_QUAD_EXP = 0, 1
+
+
+def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, n_rows: int, act: int = ACT_NONE, a: float = 0.0,
+             b: float = 0.0) -> None:
+    """out = act(x + bias) in float32.  ACT_QUAD_EXP: z > 0: a z^2 + z / 2; z <= 0: b (exp(z) - 1 - z) + z / 2."""
+    lib = _lib("core")
+    _need(x, x.dtype, "rows")
+    _need(out, x.dtype, "activation output")
+    width = x.shape[-1]
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != width:
+            raise KernelError("bias_act: the bias does not have the rows' width")
+    if out.shape[-1] != width or x.numel() < n_rows * width or out.numel() < n_rows * width:
+        raise KernelError("bias_act: widths or rows do not match")
+    _check(lib, lib.x0ne_bias_act(_ptr(x), _ptr(bias), _ptr(out), dtype_tag(x.dtype), n_rows, width, act, float(a), float(b), _stream()),
+           "bias_act")
+
+
+# ---------------------------------------------------------------------------------------------
+# linear recurrence with a matrix state per head (csrc/wkv.cu, module `core`)
+# ---------------------------------------------------------------------------------------------
+def token_shift_mix(h: torch.Tensor, mu: torch.Tensor, mixes: torch.Tensor, state: torch.Tensor, last_off: int,
+                    row_slot: torch.Tensor, row_pos: torch.Tensor, n_rows: int) -> None:
+    """mixes[s, row] = h[row] + (h_before[row] - h[row]) * mu[s]: h_before is the row above where that is the same
+    sequence's previous position, else the `width` values at `last_off` of the sequence's state row (zeros at a start)."""
+    lib = _lib("core")
+    _need(h, h.dtype, "mixer input")
+    _need(mu, torch.float32, "mix coefficients")
+    _need(mixes, h.dtype, "mixes")
+    _need(state, torch.float32, "state")
+    width = h.shape[-1]
+    n_mix = mu.shape[0]
+    if mu.shape[-1] != width or mixes.dim() != 3 or mixes.shape[0] != n_mix or mixes.shape[-1] != width or mixes.shape[1] < n_rows \
+            or h.numel() < n_rows * width or state.dim() != 2 or state.shape[1] < last_off + width:
+        raise KernelError("token_shift_mix: shapes do not match")
+    _check(lib, lib.x0ne_token_shift_mix(_ptr(h), dtype_tag(h.dtype), _ptr(mu), n_mix, _ptr(mixes), mixes.stride(0), _ptr(state),
+                                         state.stride(0), last_off, _ptr(row_slot), _ptr(row_pos), n_rows, width, _stream()),
+           "token_shift_mix")
+
+
+def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, w0: torch.Tensor, u: torch.Tensor, h: torch.Tensor,
+             o: torch.Tensor, state: torch.Tensor, seq_first_row: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int, heads: int,
+             n: int) -> None:
+    """Per sequence and head, token by token over the sequence's rows, from and into its state [heads, n, n]:
+    w = exp(-exp(z + w0)); o[j] = sum_i r[i] (S[i][j] + u[i] k[i] v[j]); S[i][j] = w[i] S[i][j] + k[i] v[j].  The last
+    row's h is left behind the matrices in the state row.  r, k, v, h in the activation type; z, o, state float32."""
+    lib = _lib("core")
+    for t, what in ((r, "r"), (k, "k"), (v, "v"), (h, "mixer input")):
+        _need(t, r.dtype, what)
+    for t, what in ((z, "decay exponents"), (w0, "decay offsets"), (u, "bonus"), (o, "scan output"), (state, "state")):
+        _need(t, torch.float32, what)
+    hn, width = heads * n, h.shape[-1]
+    if any(t.shape[-1] != hn for t in (r, k, v, z, o)) or w0.numel() != hn or u.numel() != hn or state.dim() != 2 \
+            or state.shape[1] < heads * n * n + width:
+        raise KernelError("wkv_scan: shapes do not match")
+    _check(lib, lib.x0ne_wkv_scan(_ptr(r), _ptr(k), _ptr(v), dtype_tag(r.dtype), _ptr(z), _ptr(w0), _ptr(u), _ptr(h), _ptr(o),
+                                  _ptr(state), state.stride(0), _ptr(seq_first_row), _ptr(seq_slot), n_seqs, heads, n, width,
+                                  _stream()), "wkv_scan")
+
+
+def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, n_rows: int, heads: int, n: int,
+                   eps: float) -> None:
+    """out[row, head] = o / sqrt(mean(o^2) + eps) * weight * silu(gate), per head of n values; o float32."""
+    lib = _lib("core")
+    _need(o, torch.float32, "scan output")
+    _need(weight, torch.float32, "head norm weight")
+    _need(gate, gate.dtype, "gate")
+    _need(out, gate.dtype, "gated output")
+    hn = heads * n
+    if o.shape[-1] != hn or gate.shape[-1] != hn or out.shape[-1] != hn or weight.numel() != hn or out.numel() < n_rows * hn:
+        raise KernelError("head_norm_gate: shapes do not match")
+    _check(lib, lib.x0ne_head_norm_gate(_ptr(o), _ptr(weight), _ptr(gate), _ptr(out), dtype_tag(out.dtype), n_rows, heads, n, float(eps),
+                                        _stream()), "head_norm_gate")
+
+
+def tanh_rows(x: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
+    """out = tanh(x) for the first n_rows rows; x float32."""
+    lib = _lib("core")
+    _need(x, torch.float32, "rows")
+    _need(out, out.dtype, "tanh output")
+    if out.shape[-1] != x.shape[-1] or x.numel() < n_rows * x.shape[-1] or out.numel() < n_rows * x.shape[-1]:
+        raise KernelError("tanh_rows: shapes do not match")
+    _check(lib, lib.x0ne_tanh_rows(_ptr(x), _ptr(out), dtype_tag(out.dtype), n_rows * x.shape[-1], _stream()), "tanh_rows")

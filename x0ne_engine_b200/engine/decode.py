@@ -244,6 +244,7 @@ class DeviceBatch:
         restored around it."""
         saved = [t[:n].clone() for t in self._per_row]
         saved_out = self.out_token[:n].clone()      # (the status word behind them is not touched)
+        saved_states = self.engine.cache.snapshot_states(self.row_slot[:n])     # a recurrent mixer's step is not idempotent
         torch.cuda.synchronize()
         before = ops.LAUNCHES
         self._launch(n, max_context)            # lets libraries and the workspace finish their lazy set-up
@@ -255,6 +256,7 @@ class DeviceBatch:
         for t, s in zip(self._per_row, saved):
             t[:n] = s
         self.out_token[:n] = saved_out
+        self.engine.cache.restore_states(saved_states)
         torch.cuda.synchronize()
         self.engine.ws.frozen = True      # the graph holds the buffers' addresses
         self.graphs[(n, max_context)] = g

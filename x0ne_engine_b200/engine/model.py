@@ -43,6 +43,9 @@ def tensor_needs_of_spec(spec: ModelSpec) -> List[TensorNeed]:
     for layer in spec.layers:
         for _, cls, ps in layer_part_classes(layer):
             needs += cls.tensor_needs(ps)
+    for e in spec.run_order:
+        if e.before is not None:
+            needs += P.OPENERS.get(e.before.kind).tensor_needs(e.before)
     needs += P.NORMS.get(spec.final_norm.kind).tensor_needs(spec.final_norm)
     needs += P.HEADS.get(spec.head.kind).tensor_needs(spec.head)
     return _unique(needs)
@@ -102,6 +105,9 @@ class CausalLM:
         self.blocks: List[P.Block] = []
         for layer in spec.layers:
             self.blocks.append(P.BLOCKS.get(layer.block)({role: cls(ps, env) for role, cls, ps in layer_part_classes(layer)}))
+        # what a run-order entry asks to have done to the residual right before its layer (None: nothing)
+        self.openers: List[Optional[P.Opener]] = [
+            P.OPENERS.get(e.before.kind)(e.before, env) if e.before is not None else None for e in spec.run_order]
         self.final_norm = P.NORMS.get(spec.final_norm.kind)(spec.final_norm, env)
         self.head = P.HEADS.get(spec.head.kind)(spec.head, env)
 
@@ -109,6 +115,7 @@ class CausalLM:
         out: List[P.Part] = [self.embedding] + list(self.env.positions.values())
         for b in self.blocks:
             out += b.parts()
+        out += [o for o in self.openers if o is not None]
         return out + [self.final_norm, self.head]
 
     def replayable(self) -> bool:
@@ -140,6 +147,8 @@ class CausalLM:
             pos.on_embedding(ctx, resid, ctx.n_rows)
         delta = None
         for i, e in enumerate(self.spec.run_order):
+            if self.openers[i] is not None:
+                delta = self.openers[i].forward(ctx, resid, delta, ctx.n_rows)
             delta = self.blocks[e.layer].forward(ctx, i, resid, delta, cache_entry=e.reads_cache_of,
                                                  write_cache=e.reads_cache_of is None)
         if n_want == 0:

@@ -21,6 +21,8 @@ sees the model's name or its config.json.  The kinds:
                      delta)` returns the pending delta.
   * `Embedding`    — `forward(ctx, resid, n_rows)` fills the float32 residual from the token ids.
   * `Head`         — `forward(normed, logits, n_rows)` writes float32 logits of the normed rows.
+  * `Opener`       — `forward(ctx, resid, delta, n_rows)`: runs right before a run-order entry that names one
+                     (`RunEntry.before`); adds the pending delta and whatever it brings into the residual.
 
 To add a part: subclass the kind, implement `tensor_needs(spec)` (static: the checkpoint
 tensors, by name, with shapes) and `bind(tensors)`, and call the kind's `register`.  A part that
@@ -124,6 +126,14 @@ class Embedding(Part):
         raise NotImplementedError
 
 
+class Opener(Part):
+    """Changes the float32 residual right before a run-order entry's layer: it takes the pending delta of the
+    layer before (a tensor or None), adds it, adds what it brings, and so leaves nothing pending."""
+
+    def forward(self, ctx, resid: torch.Tensor, delta, n_rows: int) -> None:
+        raise NotImplementedError
+
+
 class Head(Part):
     @staticmethod
     def optional_duplicates(spec: PartSpec) -> Dict[str, str]:
@@ -198,5 +208,6 @@ POSITIONS = Registry("position encoding")
 BLOCKS = Registry("block")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("head")
+OPENERS = Registry("opener")
 # the registry behind each kind of part a block's role may name
 PART_REGISTRIES = {"norm": NORMS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS}

@@ -20,6 +20,17 @@ class PreNormBlock(Block):
         return self.ffn.forward(ctx, normed, ctx.n_rows)
 
 
+class PreNormMixerBlock(Block):
+    """x += mixer(norm(x)) and nothing else: a pre-norm layer without a feed-forward."""
+    replayable = True
+    ROLES = {"mixer_norm": "norm", "mixer": "mixer"}
+
+    def forward(self, ctx, entry, resid, delta, cache_entry=None, write_cache=True):
+        normed = ctx.ws.buffer("normed", (ctx.ws.max_rows, resid.shape[-1]), ctx.dtype)
+        self.mixer_norm.add_norm(ctx, resid, delta, normed, ctx.n_rows)
+        return self.mixer.forward(ctx, entry, normed, ctx.n_rows, cache_entry=cache_entry, write_cache=write_cache)
+
+
 class ParallelBlock(Block):
     """x += mixer(norm(x)) + ffn(norm(x)): one norm, both branches read its output, and their results
     are summed in float32 as they are added to the residual.  The add is again fused into the next
@@ -69,5 +80,6 @@ class SandwichBlock(Block):
 
 
 BLOCKS.register("prenorm", PreNormBlock)
+BLOCKS.register("prenorm_mixer", PreNormMixerBlock)
 BLOCKS.register("sandwich", SandwichBlock)
 BLOCKS.register("parallel", ParallelBlock)

@@ -8,7 +8,7 @@ import torch
 from ..config.spec import PartSpec
 from ..csrc import ops
 from ..weights.loader import TensorNeed
-from .base import EMBEDDINGS, HEADS, Embedding, Head
+from .base import EMBEDDINGS, HEADS, OPENERS, Embedding, Head, Opener
 from .linear import Linear
 
 
@@ -33,6 +33,43 @@ class TokenEmbedding(Embedding):
 
     def forward(self, ctx, resid, n_rows):
         ops.embedding(self.table, ctx.tokens, resid, n_rows, self.scale)
+
+
+class PassOpener(Opener):
+    """The start of a pass over a stretch of layers that a model repeats:
+    resid = ((resid + pending delta) + scale * table[token]) + step[step_row], one float32 add after the other.  The
+    embedding term is the model's embedding output over again (`add_embedding`; a first pass leaves it out); `step` is a
+    [step_rows, hidden_size] tensor of which every pass has a row of its own.
+    Parameters: hidden_size, vocab_size, scale, add_embedding, step_row, step_rows, names.{table, step}."""
+    replayable = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.scale = float(spec.get("scale", 1.0) or 1.0)
+        self.add_embedding = bool(spec.get("add_embedding"))
+        self.row = int(spec["step_row"])
+        if not 0 <= self.row < int(spec["step_rows"]):
+            raise ValueError("a pass opener names a row of its step tensor that does not exist")
+        self.table = self.step = None
+
+    @staticmethod
+    def tensor_needs(spec: PartSpec) -> List[TensorNeed]:
+        h, n = int(spec["hidden_size"]), spec["names"]
+        needs = [TensorNeed(n["step"], (int(spec["step_rows"]), h), role="vector", init="linear")]
+        if spec.get("add_embedding"):
+            needs.append(TensorNeed(n["table"], (int(spec["vocab_size"]), h), init="embedding"))
+        return needs
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        n = self.spec["names"]
+        self.step = tensors[n["step"]][self.row].contiguous()
+        self.table = tensors[n["table"]] if self.add_embedding else None
+
+    def forward(self, ctx, resid, delta, n_rows):
+        if delta is not None and not isinstance(delta, torch.Tensor):
+            raise ValueError("a pass opener takes the pending result of a layer as one tensor")
+        ops.open_pass(resid, delta, self.table, ctx.tokens if self.add_embedding else None, self.scale, self.step, n_rows)
+        return None
 
 
 class LMHead(Head):
@@ -67,3 +104,4 @@ class LMHead(Head):
 
 EMBEDDINGS.register("token_embedding", TokenEmbedding)
 HEADS.register("lm_head", LMHead)
+OPENERS.register("pass_opener", PassOpener)

@@ -19,7 +19,10 @@ class RoutedExperts(FeedForward):
     choice is made on s + correction: the outputs form `groups` equal groups of neighbours, a group
     is worth its largest such value, only the `keep_groups` best groups can give experts, and of
     those the `top` largest values are chosen; the weights are the chosen outputs' scores s, not
-    renormalized.  An expert is down(act(up x)) with act the squared ReLU, no biases.  The last
+    renormalized.  With `choice` "logits" there is no softmax over all outputs: the `top` largest z + correction (the
+    correction is then the router's bias) are chosen and the weights are the softmax over the chosen values alone.
+    An expert is down(act(up x)) with act the squared ReLU, or, with `activation` "swiglu",
+    down(silu(gate x) * up x) (gate and up packed per expert, gate rows first); no biases.  The last
     `identity` router outputs are identity experts: they return x itself and have no tensors.  The
     shared expert has the same form with a width of its own, runs for every row, and is multiplied
     by the sigmoid of one more projection of x (`shared_gate`).
@@ -31,8 +34,8 @@ class RoutedExperts(FeedForward):
     the choices.
 
     Parameters: hidden_size, experts, identity, top, groups, keep_groups, expert_size, activation
-    ("relu2"), shared_size (None: no shared expert), shared_gate, names.{router, correction, up, down
-    (patterns with {e}), shared_up, shared_down, shared_gate}.
+    ("relu2" | "swiglu"), choice ("scores" | "logits"), shared_size (None: no shared expert), shared_gate,
+    names.{router, correction, gate, up, down (patterns with {e}), shared_up, shared_down, shared_gate}.
     """
     replayable = True
 
@@ -49,8 +52,15 @@ class RoutedExperts(FeedForward):
         self.inter = int(spec["expert_size"])
         self.shared_size = int(g("shared_size") or 0)
         self.shared_gate = bool(g("shared_gate")) and self.shared_size > 0
-        if g("activation", "relu2") != "relu2":
-            raise ValueError(f"expert activation {g('activation')!r} is not served; served: 'relu2'")
+        self.activation = g("activation", "relu2") or "relu2"
+        if self.activation not in ("relu2", "swiglu"):
+            raise ValueError(f"expert activation {self.activation!r} is not served; served: 'relu2', 'swiglu'")
+        self.gated = self.activation == "swiglu"
+        self.choice = g("choice", "scores") or "scores"
+        if self.choice not in ("scores", "logits"):
+            raise ValueError(f"router choice {self.choice!r} is not served; served: 'scores', 'logits'")
+        if self.gated and self.shared_size:
+            raise ValueError("a shared expert beside gated experts is not served")
         if self.n_out % self.groups or not 1 <= self.keep_groups <= self.groups or \
                 not 1 <= self.top <= self.keep_groups * (self.n_out // self.groups):
             raise ValueError(f"{self.n_out} router outputs in {self.groups} groups of which {self.keep_groups} stay cannot "
@@ -62,7 +72,10 @@ class RoutedExperts(FeedForward):
         h, n = int(spec["hidden_size"]), spec["names"]
         E, I, ff = int(spec["experts"]), int(spec.get("identity") or 0), int(spec["expert_size"])
         needs = []
+        gated = (spec.get("activation") or "relu2") == "swiglu"
         for e in range(E):
+            if gated:
+                needs.append(TensorNeed(n["gate"].format(e=e), (ff, h)))
             needs += [TensorNeed(n["up"].format(e=e), (ff, h)), TensorNeed(n["down"].format(e=e), (h, ff))]
         needs += [TensorNeed(n["router"], (E + I, h)), TensorNeed(n["correction"], (E + I,), role="vector", init="linear")]
         sf = int(spec.get("shared_size") or 0)
@@ -77,7 +90,11 @@ class RoutedExperts(FeedForward):
         rows = [tensors[n["router"]]] + ([tensors[n["shared_gate"]]] if self.shared_gate else [])
         self.router = Linear(torch.cat(rows, dim=0).contiguous())
         self.correction = tensors[n["correction"]]
-        self.up = torch.stack([tensors[n["up"].format(e=e)] for e in range(self.experts)]).contiguous()       # [E, ff, hidden]
+        if self.gated:      # [E, 2 ff, hidden]: an expert's gate rows, then its up rows
+            self.up = torch.stack([torch.cat([tensors[n["gate"].format(e=e)], tensors[n["up"].format(e=e)]], dim=0)
+                                   for e in range(self.experts)]).contiguous()
+        else:
+            self.up = torch.stack([tensors[n["up"].format(e=e)] for e in range(self.experts)]).contiguous()   # [E, ff, hidden]
         self.down = torch.stack([tensors[n["down"].format(e=e)] for e in range(self.experts)]).contiguous()   # [E, hidden, ff]
         if self.shared_size:
             self.shared_up = Linear(tensors[n["shared_up"]])
@@ -106,9 +123,11 @@ class RoutedExperts(FeedForward):
         y = ws.buffer("moe.y", (rows * top, self.hidden), torch.float32)
         out = ws.buffer(self.out_buffer, (rows, self.hidden), dt)
         self.router(x, z, n_rows)
-        ops.moe_route(z, self.correction, self.n_out, self.groups, self.keep_groups, top, n_rows, chosen, weights, sgate, self.n_out)
+        ops.moe_route(z, self.correction, self.n_out, self.groups, self.keep_groups, top, n_rows, chosen, weights, sgate, self.n_out,
+                      on_logits=self.choice == "logits")
         pairs = n_rows * top
-        if ops.moe_tc_takes(dt, pairs, self.hidden, self.inter):
+        up_kind = 2 if self.gated else 0
+        if not self.gated and ops.moe_tc_takes(dt, pairs, self.hidden, self.inter):
             # many pairs: tiles of 128 listed pairs on the tensor cores; the rows are gathered into the listed order first,
             # the activations stay in that order, the down product writes by pair
             n_tiles = ops.moe_max_tiles(pairs, self.experts, ops.MOE_TC_TILE_ROWS)
@@ -120,7 +139,7 @@ class RoutedExperts(FeedForward):
         else:
             n_tiles = ops.moe_max_tiles(pairs, self.experts)
             ops.moe_group(chosen, pairs, self.experts, offsets, listed, tiles[:n_tiles])
-            ops.moe_product(0, x, self.up, listed, tiles, n_tiles, top, act)
+            ops.moe_product(up_kind, x, self.up, listed, tiles, n_tiles, top, act)
             ops.moe_product(1, act, self.down, listed, tiles, n_tiles, top, y)
         shared = None
         if self.shared_size:
