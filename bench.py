@@ -13,9 +13,9 @@ time); `e2e` is the same rate through `Model.generate` with host token lists in 
 and 64 and the milliseconds a 128-token and a 512-token prompt take through the step function; `roofline` places the decode step against the bytes it must read.  One JSON line is
 printed.  This library runs on one GPU: for --gpus above 1 a line says so and the exit code is 2.
 
-    python bench.py --design rovurax|tenetar [--sizes 1.7b,8b] [--layers 8] [--chunk 1024] [--steps K]
+    python bench.py --design rovurax|tenetar|retuvik [--sizes 1.7b,8b] [--layers 8] [--chunk 1024] [--steps K]
 
-instead runs that design beside Qwen3 at equal sizes (random bfloat16 weights, the same engine,
+instead runs that design beside Qwen3 (retuvik: beside Tenetar) at equal sizes (random bfloat16 weights, the same engine,
 step function and decode graphs): one prompt of --prefill-tokens through the step function, then decode
 at --batch, device-timed; one JSON line with a row per size and design.
 """
@@ -167,6 +167,28 @@ def tenetar_config(size: dict, layers: int, vocab: int, window: int):
                              "embedding": {"scale": float(w) ** 0.5}, "layers": out})
 
 
+def retuvik_config(size: dict, layers: int, vocab: int, window: int):
+    """A Retuvik configuration of the given layer sizes.  Of every four layers three are recurrent (heads of 64
+    channels that fill the width, a decay of inner width 64) and the fourth is windowed attention with the distance
+    bias, query temperature and output gate; the first layer has a dense feed-forward of the full width, the others
+    16 gated experts of a sixth of it, 4 chosen per token: the dense layer's products per token.  The whole list is a
+    stretch that runs once, so a pass opener runs; norms in 4 groups."""
+    from x0ne_engine_b200.config import config_from_dict
+    w, ff, H, G, d = size["width"], size["ff"], size["heads"], size["kv_heads"], size["dim"]
+    moe = {"kind": "moe", "expert": {"ff": ff // 6}, "router": {"experts": 16, "top": 4}}
+    out = []
+    for i in range(layers):
+        if i % 4 == 3:
+            layer = {"type": "attention", "mixer": {"dim": d, "heads": H, "kv_heads": G, "vdim": d, "scale": d ** -0.5, "mask": {"size": window},
+                                                    "q_temp": {"coef": 0.1, "every": 1024}}}
+        else:
+            layer = {"type": "wkv", "mixer": {"dim": 64, "heads": w // 64, "decay_rank": 64}}
+        layer["mlp"] = {"kind": "dense", "ff": ff} if i == 0 else moe
+        out.append(layer)
+    return config_from_dict({"architecture": "Retuvik", "vocab": vocab, "width": w, "norm": {"eps": 1e-6, "groups": 4},
+                             "embedding": {"scale": float(w) ** 0.5}, "layers": out, "loop": {"start": 0, "stop": layers, "times": 1}})
+
+
 def design_configs(size: dict, layers: int, vocab: int, chunk: int, design: str = "rovurax"):
     """(the design's configuration, Qwen3 configuration) with the same width, heads, feed-forward, depth and
     vocabulary.  Of every four Rovurax layers three are chunk-masked attention with blended values and
@@ -179,6 +201,8 @@ def design_configs(size: dict, layers: int, vocab: int, chunk: int, design: str 
                         rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, dtype="bfloat16")
     if design == "tenetar":
         return tenetar_config(size, layers, vocab, chunk), old
+    if design == "retuvik":        # beside the closest design the library has: Tenetar (windowed attention, routed experts)
+        return retuvik_config(size, layers, vocab, chunk), tenetar_config(size, layers, vocab, chunk)
     mlp = {"ff": ff, "kind": "dense", "limit": 7.0}
     att = {"type": "attention", "mlp": mlp, "mixer": {"dim": d, "heads": H, "kv_heads": G, "vdim": d, "scale": d ** -0.5,
                                                         "mask": {"size": chunk}, "v_mix": True}}
@@ -205,9 +229,10 @@ def design_bench(args) -> int:
     layers = args.layers or 8
     vocab = 32768
     rows_out = []
+    other = "tenetar" if args.design == "retuvik" else "qwen3"
     for name in args.sizes.split(","):
         size = DESIGN_SIZES[name]
-        for design, cfg in zip((args.design, "qwen3"), design_configs(size, layers, vocab, args.chunk, args.design)):
+        for design, cfg in zip((args.design, other), design_configs(size, layers, vocab, args.chunk, args.design)):
             model = x.Model.random(cfg, seed=0, dtype="bfloat16", max_batch=B, max_ctx=ctx, max_step_tokens=max(T, 64))
             eng = model.engine
             ids = synthetic_ids(T, vocab, 20261104)
@@ -247,17 +272,20 @@ def design_bench(args) -> int:
             finally:
                 runner.close()
             weight_bytes, kv_per_tok = eng.model.step_weight_bytes(), eng.cache.bytes_per_token()
-            step_bytes = weight_bytes + B * (T + W + K / 2.0) * kv_per_tok
+            # fixed-size states (a recurrent layer's matrices) are read and written once per sequence and step
+            state_bytes = sum(t[0].numel() * 4 for t in {id(t): t for t in eng.cache.states.values()}.values())
+            step_bytes = weight_bytes + B * (T + W + K / 2.0) * kv_per_tok + 2.0 * B * state_bytes
             rows_out.append({"size": name, "design": design, "layers": layers, "prefill_tokens": T, "prefill_ms": pre_ms,
                              "prefill_tok_s": T / (pre_ms / 1e3), "decode_batch": B, "decode_ms_per_step": dec_ms,
                              "decode_tok_s": B / (dec_ms / 1e3), "decode_bytes_per_step": step_bytes,
                              "decode_frac_of_hbm": step_bytes / (dec_ms / 1e3) / 1e9 / pk["hbm_gbs"],
-                             "launches_per_decode_step": launches, "cache_bytes_per_token": kv_per_tok})
+                             "launches_per_decode_step": launches, "cache_bytes_per_token": kv_per_tok,
+                             "state_bytes_per_sequence": state_bytes})
             print(f"[bench] {name} {design}: prefill {T} tokens {pre_ms:.2f} ms, decode b{B} {dec_ms:.3f} ms/step "
                   f"({rows_out[-1]['decode_frac_of_hbm']:.2f} of {pk['source']} copy bandwidth)", file=sys.stderr, flush=True)
             del runner, model, eng
             torch.cuda.empty_cache()
-    print(json.dumps({"metric": f"prefill and decode tokens/s of {args.design.capitalize()} beside Qwen3 at equal sizes (random bf16 weights)",
+    print(json.dumps({"metric": f"prefill and decode tokens/s of {args.design.capitalize()} beside {other.capitalize()} at equal sizes (random bf16 weights)",
                       "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "dtype": "bf16", "data": "synthetic",
                       "impl": "ours", "chunk": args.chunk, "peaks": pk, "rows": rows_out}))
     return 0
@@ -275,11 +303,11 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--design", default=None, choices=["rovurax", "tenetar"],
-                    help="instead of the default workload: this design beside Qwen3 at equal sizes (prefill and decode)")
+    ap.add_argument("--design", default=None, choices=["rovurax", "tenetar", "retuvik"],
+                    help="instead of the default workload: this design beside Qwen3 (retuvik: beside Tenetar) at equal sizes (prefill and decode)")
     ap.add_argument("--sizes", default="1.7b,8b", help="with --design: which of " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--chunk", type=int, default=1024,
-                    help="with --design: positions per chunk of the masked attention (rovurax) or of the sliding window (tenetar)")
+                    help="with --design: positions per chunk of the masked attention (rovurax) or of the sliding window (tenetar, retuvik)")
     args = ap.parse_args()
     if args.design is not None and args.impl == "ours" and args.gpus == 1:
         return design_bench(args)

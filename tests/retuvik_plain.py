@@ -108,7 +108,8 @@ def attention_mixer(h: torch.Tensor, mixer: Mapping, t: Mapping[str, torch.Tenso
                     start: int = 0, past: Optional[Dict] = None) -> torch.Tensor:
     """Grouped-query attention over the rows of h [T, W], positions start .. start + T - 1.  `past` (a dict)
     holds the keys and values of the positions before `start` and gets those of these rows appended."""
-    H, G, D, Dv = mixer["heads"], mixer["kv_heads"], mixer["dim"], mixer["vdim"]
+    H, D = mixer["heads"], mixer["dim"]
+    G, Dv = mixer.get("kv_heads") or H, mixer.get("vdim") or D
     T = h.shape[0]
     pos = torch.arange(start, start + T)
     q = unit_rms((h @ f32(t[p + "q"]).T).view(T, H, D), eps) * f32(t[p + "q.norm"])
@@ -168,12 +169,15 @@ def expert(h: torch.Tensor, t: Mapping[str, torch.Tensor], p: str) -> torch.Tens
 
 
 def moe_ff(h: torch.Tensor, mlp: Mapping, t: Mapping[str, torch.Tensor], p: str, margins: Optional[List] = None,
-           forced: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """`margins` collects, per row, the gap between the last chosen logit and the first one left out.  `forced`
-    [T, top] replaces the choice (the weights are then the softmax over the forced experts' logits)."""
+           forced: Optional[torch.Tensor] = None, own: Optional[List] = None) -> torch.Tensor:
+    """`margins` collects, per row, the gap between the last chosen logit and the first one left out, `own` the
+    choice made here.  `forced` [T, top] replaces the choice (the weights are then the softmax over the forced
+    experts' logits)."""
     top = mlp["router"]["top"]
     z = router_logits(h, t, p)
     idx, wt = choose(z, top)
+    if own is not None:
+        own.append(idx.clone())
     if margins is not None:
         s = torch.sort(z, dim=-1, descending=True).values
         margins.append((s[:, top - 1] - s[:, top]) if z.shape[1] > top else torch.full((z.shape[0],), float("inf")))
@@ -202,9 +206,10 @@ def run_order(cfg: Mapping):
 
 
 def forward(cfg: Mapping, t: Mapping[str, torch.Tensor], ids, layers_out: Optional[List] = None, margins=None, forced=None,
-            states: Optional[List[Dict]] = None, start: int = 0) -> torch.Tensor:
+            states: Optional[List[Dict]] = None, start: int = 0, own=None) -> torch.Tensor:
     """Logits [T, vocab] of the tokens `ids` at positions start ..; `states` (one dict per layer run, kept by the
-    caller) carries a sequence from one call to the next."""
+    caller) carries a sequence from one call to the next.  `forced`, `margins` and `own` count the routed feed-forwards
+    in the order they run (a repeated layer counts each time)."""
     eps, groups = cfg["norm"]["eps"], cfg["norm"].get("groups", 1)
     ids = torch.as_tensor(list(ids), dtype=torch.int64)
     emb = f32(t["embed"])[ids] * (cfg.get("embedding") or {}).get("scale", 1.0)
@@ -230,7 +235,7 @@ def forward(cfg: Mapping, t: Mapping[str, torch.Tensor], ids, layers_out: Option
             if mlp["kind"] == "dense":
                 x = x + dense_ff(h, t, p + "mlp.")
             else:
-                x = x + moe_ff(h, mlp, t, p + "mlp.", margins, None if forced is None else forced[moe_at])
+                x = x + moe_ff(h, mlp, t, p + "mlp.", margins, None if forced is None else forced[moe_at], own)
                 moe_at += 1
         if layers_out is not None:
             layers_out.append(x.clone())

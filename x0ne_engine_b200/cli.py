@@ -529,6 +529,65 @@ def cmd_kernel_bench(a) -> int:
         distinct = int(torch.unique(chosen).numel())
         timed(run, distinct * 2 * ff * hidden * 2 + pairs * (hidden * 2 * 2 + ff * 2 * 2 + hidden * 4), 4.0 * pairs * ff * hidden)
         return 0
+    if a.kernel in ("wkv_scan", "token_shift", "head_norm_gate"):
+        # the recurrent mixer's own kernels: --batch sequences of --m rows each, --q-heads heads of --head-dim channels,
+        # --k the model's width; every sequence goes on from its state (m 1: a decode step)
+        B, per, heads, n, width = a.batch, a.m, a.q_heads, a.head_dim, a.k
+        rows, hn, mats = B * per, heads * n, heads * n * n
+        bf = lambda *shape: torch.randn(*shape, device=dev).bfloat16()          # noqa: E731
+        state = torch.randn(B, mats + width, device=dev).mul_(0.1)
+        row_slot = torch.arange(B, dtype=torch.int32, device=dev).repeat_interleave(per).contiguous()
+        row_pos = (torch.arange(per, dtype=torch.int32, device=dev) + 7).repeat(B).contiguous()
+        h = bf(rows, width)
+        copies = 1
+        if a.kernel == "token_shift":
+            mu = torch.rand(5, width, device=dev)
+            mixes = torch.empty(5, rows, width, device=dev, dtype=torch.bfloat16)
+            timed(lambda: ops.token_shift_mix(h, mu, mixes, state, mats, row_slot, row_pos, rows), rows * width * 2 * 6)
+            return 0
+        o = torch.randn(rows, hn, device=dev)
+        if a.kernel == "head_norm_gate":
+            gate, out, w = bf(rows, hn), torch.empty(rows, hn, device=dev, dtype=torch.bfloat16), torch.ones(hn, device=dev)
+            timed(lambda: ops.head_norm_gate(o, w, gate, out, rows, heads, n, 1e-6), rows * hn * (4 + 2 + 2))
+            return 0
+        r, k, v, z = bf(rows, hn), bf(rows, hn), bf(rows, hn), torch.randn(rows, hn, device=dev)
+        w0, u = torch.randn(hn, device=dev) - 2.0, torch.randn(hn, device=dev)
+        first = (torch.arange(B + 1, dtype=torch.int32, device=dev) * per).contiguous()
+        slots = torch.arange(B, dtype=torch.int32, device=dev)
+        timed(lambda: ops.wkv_scan(r, k, v, z, w0, u, h, o, state, first, slots, B, heads, n),
+              rows * hn * (3 * 2 + 4 + 4) + 2 * B * mats * 4, 4.0 * rows * hn * n)
+        return 0
+    if a.kernel == "head_norm_kv":
+        # per-head norms of queries and keys, query temperature, unit values, keys and values into the pages; --m rows
+        from .cache import SequenceCache
+        from .parts.base import CacheNeed
+        rows, qh, kvh, hd = a.m, a.q_heads, a.kv_heads, a.head_dim
+        cache = SequenceCache([CacheNeed("kv", kvh, hd, None)], [None], rows + 64, rows + 64, torch.bfloat16, dev)
+        slot = cache.acquire(rows)
+        width = (2 * qh + 2 * kvh) * hd                       # q, k, v and the gate's columns in one projection
+        src = torch.randn(rows, width, device=dev).bfloat16()
+        q_out = torch.empty(rows, qh * hd, device=dev, dtype=torch.bfloat16)
+        wq, wk = torch.ones(hd, device=dev), torch.ones(hd, device=dev)
+        slots = torch.full((rows,), slot, dtype=torch.int32, device=dev)
+        pos = torch.arange(rows, dtype=torch.int32, device=dev)
+        copies = 1
+        timed(lambda: ops.head_norm_kv_write(src, qh * hd, (qh + kvh) * hd, wq, wk, 1e-6, 0.1, 1024, True, q_out, qh, cache.kv_view(0),
+                                             slots, pos, rows), rows * ((qh + 2 * kvh) * hd * 2 + qh * hd * 2 + 2 * kvh * hd * 2))
+        return 0
+    if a.kernel in ("group_rmsnorm", "bias_act"):
+        rows, h = a.m, a.n
+        copies = 1
+        if a.kernel == "bias_act":
+            x, bias = torch.randn(rows, h, device=dev).bfloat16(), torch.randn(h, device=dev)
+            out = torch.empty_like(x)
+            timed(lambda: ops.bias_act(x, bias, out, rows, ops.ACT_QUAD_EXP, 0.7, 1.1), rows * h * 4)
+            return 0
+        resid = torch.randn(rows, h, device=dev)
+        delta = torch.randn(rows, h, device=dev).bfloat16()
+        w = torch.ones(h, device=dev)
+        out = torch.empty_like(delta)
+        timed(lambda: ops.add_rmsnorm(resid, delta, w, out, rows, 1e-6, groups=4), rows * h * (4 + 4 + 2 + 2))
+        return 0
     if a.kernel == "add_normed_rmsnorm":
         rows, h = a.m, a.n
         resid = torch.randn(rows, h, device=dev)
