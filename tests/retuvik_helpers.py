@@ -245,7 +245,7 @@ def agreement(cfg, tensors, ids, forced, clear=0.25):
         ok = m >= clear
         same_all += int(eq.sum()); n_all += eq.numel()
         same_clear += int((eq & ok).sum()); n_clear += int(ok.sum())
-    return same_all / max(n_all, 1), same_clear / max(n_clear, 1)
+    return same_all / max(n_all, 1), (same_clear / n_clear if n_clear else 1.0)
 
 
 def clear_ids(cfg, tensors, n, seed=0, margin=0.0):

@@ -234,6 +234,139 @@ def test_router_choice_on_logits(n, top):
     assert (weights.sum(-1).cpu() - 1).abs().max() <= 1e-6
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,E,top,hidden,ff", [(1, 4, 2, 64, 40), (9, 6, 3, 72, 128), (150, 3, 2, 104, 50), (700, 16, 4, 256, 384), (513, 3, 1, 320, 256)])
+def test_gated_experts_over_grouped_pairs(dtype, rows, E, top, hidden, ff):
+    """down(silu(gate x) * up x) over the listed (row, choice) pairs against a loop over rows and choices: on the CUDA
+    cores (float32, and bfloat16 where the tensor-core kernel does not take the shape) and on tcgen05, with gate and up
+    rows packed one after the other or in blocks; experts with no pair and with more than a tile of them."""
+    from x0ne_engine_b200.csrc import ops
+    g = torch.Generator().manual_seed(rows)
+    x = torch.randn(rows, hidden, generator=g).to(dtype)
+    gate = (torch.randn(E, ff, hidden, generator=g) * (1.5 / hidden ** 0.5)).to(dtype)
+    up = (torch.randn(E, ff, hidden, generator=g) / hidden ** 0.5).to(dtype)
+    down = (torch.randn(E, hidden, ff, generator=g) / ff ** 0.5).to(dtype)
+    prefer = torch.rand(E, generator=g) ** 3
+    if E > top:
+        prefer[E - 1] = 0                                  # the last expert gets no pair at all
+    chosen = torch.stack([torch.multinomial(prefer + 1e-9 * (torch.arange(E) != E - 1), top, generator=g) for _ in range(rows)]).to(torch.int32)
+    weights = torch.rand(rows, top, generator=g)
+    pairs = rows * top
+    block = ops.MOE_PAIR_BLOCK if ff % ops.MOE_PAIR_BLOCK == 0 else 0
+    if block:
+        packed = torch.cat([gate.reshape(E, -1, block, hidden), up.reshape(E, -1, block, hidden)], dim=2).reshape(E, 2 * ff, hidden)
+    else:
+        packed = torch.cat([gate, up], dim=1)
+    tc = bool(block) and ops.moe_tc_takes(dtype, pairs, hidden, ff)
+    tile = ops.MOE_TC_TILE_ROWS if tc else ops.MOE_TILE_ROWS
+    n_tiles = ops.moe_max_tiles(pairs, E, tile)
+    i32 = lambda *shape: torch.empty(shape, dtype=torch.int32, device=DEV)
+    offsets, listed, tiles, n_real = i32(E + 1), i32(pairs), i32(n_tiles, 3), i32(1)
+    act = torch.empty((pairs, ff), dtype=dtype, device=DEV)
+    y = torch.empty((pairs, hidden), dtype=torch.float32, device=DEV)
+    out = torch.empty((rows, hidden), dtype=dtype, device=DEV)
+    xd, ch = x.to(DEV), chosen.to(DEV)
+    ops.moe_group(ch, pairs, E, offsets, listed, tiles, tile, n_real)
+    if tc:
+        xs = torch.full((pairs, hidden), float("nan"), dtype=dtype, device=DEV)
+        ops.moe_gather_rows(xd, listed, offsets, E, top, xs, pairs)
+        ops.moe_product_tc(2, xs, packed.to(DEV), listed, tiles, n_real, n_tiles, act)
+        ops.moe_product_tc(1, act, down.to(DEV), listed, tiles, n_real, n_tiles, y)
+        ops.check_tc_status(torch.device(DEV))
+    else:
+        ops.moe_product(2, xd, packed.to(DEV), listed, tiles, n_tiles, top, act, block)
+        ops.moe_product(1, act, down.to(DEV), listed, tiles, n_tiles, top, y)
+    ops.moe_combine(y, xd, ch, weights.to(DEV), top, E, None, None, out, rows)
+    want = torch.zeros(rows, hidden, dtype=torch.float64)
+    for r in range(rows):
+        for j in range(top):
+            e = int(chosen[r, j])
+            a = (torch.nn.functional.silu(gate[e].double() @ x[r].double()) * (up[e].double() @ x[r].double())).to(dtype).double()
+            want[r] += weights[r, j].double() * (a @ down[e].double().T)
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -7
+    assert (out.double().cpu() - want).abs().max() <= tol * want.abs().max()
+    if dtype == torch.bfloat16 and rows >= 500:
+        assert tc                                          # these shapes are the tensor-core kernel's
+
+
+SLOPE_CASES = [  # q_heads, kv_heads, dk, dv, window
+    (4, 2, 48, None, 100),
+    (6, 2, 20, 12, 37),
+    (3, 3, 24, 40, 64),
+    (20, 1, 16, 80, 9),
+    (8, 2, 64, 64, None),
+    (2, 1, 128, 128, 300),
+]
+
+
+@pytest.mark.parametrize("case", SLOPE_CASES)
+def test_attention_kernels_with_distance_bias_and_a_gate_per_value(case):
+    """The general bfloat16 kernels (prompt tiles; decode with one split and with several) and the plain kernel in
+    float32, against full score matrices in double precision: slope_h (i - j) off every score, the window, and
+    sigmoid gates per (row, head, value) that lie inside a wider buffer."""
+    from x0ne_engine_b200.cache import SequenceCache
+    from x0ne_engine_b200.csrc import ops
+    from x0ne_engine_b200.parts.base import CacheNeed
+    H_, G, D, Dv, window = case
+    Dv = Dv or D
+    g = torch.Generator().manual_seed(H_ * 100 + D)
+    T, scale = 330, 1.7 * D ** -0.5
+    q = (1.5 * torch.randn(T, H_, D, generator=g)).bfloat16()
+    k = torch.randn(T, G, D, generator=g).bfloat16()
+    v = torch.randn(T, G, Dv, generator=g).bfloat16()
+    gate_ld = H_ * Dv + 24
+    gate = (2 * torch.randn(T, gate_ld, generator=g)).bfloat16()
+    sl = P.slopes(H_)
+    i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+    ok = (j <= i) & ((i - j < window) if window else True)
+    want = torch.zeros(T, H_, Dv, dtype=torch.float64)
+    for h in range(H_):
+        s = (q[:, h].double() @ k[:, h // (H_ // G)].double().T) * scale - sl[h] * (i - j).double()
+        want[:, h] = torch.softmax(s.masked_fill(~ok, float("-inf")), -1) @ v[:, h // (H_ // G)].double()
+    want = want * torch.sigmoid(gate[:, :H_ * Dv].double().view(T, H_, Dv))
+    for dtype in (torch.bfloat16, torch.float32):
+        cache = SequenceCache([CacheNeed("kv", G, D, None, v_dim=None if Dv == D else Dv)], [None], 1024, 1024, dtype, DEV)
+        slot = cache.acquire(T)
+        view = cache.kv_view(0)
+        g0 = cache.groups[0]
+        store = g0.storage[0].reshape(g0.n_pages, -1)
+        for p0 in range(0, T, 64):                        # keys [kv head][64][D], then values [kv head][64][Dv] per page
+            page, n = int(g0.table_host[slot, p0 // 64]), min(64, T - p0)
+            kp = torch.zeros(G, 64, D, dtype=dtype)
+            vp = torch.zeros(G, 64, Dv, dtype=dtype)
+            kp[:, :n], vp[:, :n] = k[p0:p0 + n].transpose(0, 1).to(dtype), v[p0:p0 + n].transpose(0, 1).to(dtype)
+            store[page] = torch.cat([kp.reshape(-1), vp.reshape(-1)]).to(DEV)
+        qd, gd = q.reshape(T, H_ * D).to(dtype).to(DEV), gate.to(dtype).to(DEV)
+        slope = sl.float().to(DEV)
+        extra = ops.attn_extra(gate=gd, gate_ld=gate_ld, gate_wide=True, slope=slope)
+        slots = torch.full((T,), slot, dtype=torch.int32, device=DEV)
+        pos = torch.arange(T, dtype=torch.int32, device=DEV)
+        tol = 2e-5 if dtype == torch.float32 else 2 ** -6
+        out = torch.zeros((T, H_ * Dv), dtype=dtype, device=DEV)
+        ops.attention_rows(qd, out, view, slots, pos, T, H_, scale, window or 0, extra)
+        assert (out.double().cpu().view(T, H_, Dv) - want).abs().max() <= tol * want.abs().max(), ("plain", dtype)
+        if dtype != torch.bfloat16:
+            continue
+        assert ops.attention_flex_takes(view, dtype, 0, False) and ops.attention_flex_takes(view, dtype, 0, True)
+        # prompt tiles of 128 rows: the sequence in two portions (200 rows from position 0, then 130 more)
+        out = torch.zeros((T, H_ * Dv), dtype=dtype, device=DEV)
+        for first, n in ((0, 200), (200, 130)):
+            n_t = -(-n // 128)
+            tile_seq = torch.zeros(n_t, dtype=torch.int32, device=DEV)
+            tile_row0 = (torch.arange(n_t, dtype=torch.int32, device=DEV) * 128).contiguous()
+            ex = ops.attn_extra(gate=gd[first:], gate_ld=gate_ld, gate_wide=True, slope=slope)
+            ops.attention_flex_prefill(qd[first:first + n], out[first:first + n], view, tile_seq, tile_row0, n_t,
+                                       torch.tensor([0, n], dtype=torch.int32, device=DEV), torch.tensor([slot], dtype=torch.int32, device=DEV),
+                                       torch.tensor([first], dtype=torch.int32, device=DEV), H_, scale, window or 0, ex)
+        assert (out.double().cpu().view(T, H_, Dv) - want).abs().max() <= tol * want.abs().max(), "prompt tiles"
+        # every row as a decode row of its own
+        for splits in (1, 3):
+            out = torch.zeros((T, H_ * Dv), dtype=dtype, device=DEV)
+            scratch = torch.empty(ops.attention_flex_scratch_bytes(T, H_, G, Dv, splits) // 4 + 16, dtype=torch.float32, device=DEV) if splits > 1 else None
+            ops.attention_flex_decode(qd, out, view, slots, pos, T, H_, scale, window or 0, extra, splits, scratch)
+            assert (out.double().cpu().view(T, H_, Dv) - want).abs().max() <= tol * want.abs().max(), ("decode", splits)
+
+
 # ------------------------------------------------------------------------------------------ the recurrence's kernels
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_token_shift_blends(dtype):

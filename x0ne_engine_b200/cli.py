@@ -500,14 +500,16 @@ def cmd_kernel_bench(a) -> int:
         # --m rows, --k width, --n expert width, --experts, --top; every row chooses --top different experts at random
         rows, hidden, ff, E, top = a.m, a.k, a.n, a.experts, a.top
         pairs = rows * top
-        wbytes = 2 * E * ff * hidden * 2
+        mats = 3 if a.gated else 2                      # --gated: silu(gate x) * up x experts, gate and up rows packed in blocks
+        kind = 2 if a.gated else 0
+        wbytes = mats * E * ff * hidden * 2
         copies = max(2, int(math.ceil(256e6 / wbytes)) + 1)
-        ups = [torch.randn(E, ff, hidden, device=dev).mul_(0.02).bfloat16() for _ in range(copies)]
+        ups = [torch.randn(E, (mats - 1) * ff, hidden, device=dev).mul_(0.02).bfloat16() for _ in range(copies)]
         downs = [torch.randn(E, hidden, ff, device=dev).mul_(0.02).bfloat16() for _ in range(copies)]
         x = torch.randn(rows, hidden, device=dev).bfloat16()
         chosen = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(rows)]).to(torch.int32).contiguous()
         i32 = lambda *shape: torch.empty(shape, dtype=torch.int32, device=dev)      # noqa: E731
-        tc = ops.moe_tc_takes(torch.bfloat16, pairs, hidden, ff)
+        tc = ops.moe_tc_takes(torch.bfloat16, pairs, hidden, ff) and (not a.gated or ff % ops.MOE_PAIR_BLOCK == 0)
         tile = ops.MOE_TC_TILE_ROWS if tc else ops.MOE_TILE_ROWS
         n_tiles = ops.moe_max_tiles(pairs, E, tile)
         offsets, listed, tiles, n_real = i32(E + 1), i32(pairs), i32(n_tiles, 3), i32(1)
@@ -521,13 +523,13 @@ def cmd_kernel_bench(a) -> int:
             ops.moe_group(chosen, pairs, E, offsets, listed, tiles, tile, n_real)
             if tc:
                 ops.moe_gather_rows(x, listed, offsets, E, top, xs, pairs)
-                ops.moe_product_tc(0, xs, ups[i], listed, tiles, n_real, n_tiles, act)
+                ops.moe_product_tc(kind, xs, ups[i], listed, tiles, n_real, n_tiles, act)
                 ops.moe_product_tc(1, act, downs[i], listed, tiles, n_real, n_tiles, y)
             else:
-                ops.moe_product(0, x, ups[i], listed, tiles, n_tiles, top, act)
+                ops.moe_product(kind, x, ups[i], listed, tiles, n_tiles, top, act, ops.MOE_PAIR_BLOCK if ff % ops.MOE_PAIR_BLOCK == 0 else 0)
                 ops.moe_product(1, act, downs[i], listed, tiles, n_tiles, top, y)
         distinct = int(torch.unique(chosen).numel())
-        timed(run, distinct * 2 * ff * hidden * 2 + pairs * (hidden * 2 * 2 + ff * 2 * 2 + hidden * 4), 4.0 * pairs * ff * hidden)
+        timed(run, distinct * mats * ff * hidden * 2 + pairs * (hidden * 2 * 2 + ff * 2 * 2 + hidden * 4), 2.0 * mats * pairs * ff * hidden)
         return 0
     if a.kernel in ("wkv_scan", "token_shift", "head_norm_gate"):
         # the recurrent mixer's own kernels: --batch sequences of --m rows each, --q-heads heads of --head-dim channels,
@@ -904,6 +906,7 @@ def main(argv=None) -> int:
     k.add_argument("--layers", type=int, default=36, help="decode_step (--impl reference): layers of the model")
     k.add_argument("--vocab", type=int, default=151936, help="decode_step (--impl reference): vocabulary")
     k.add_argument("--experts", type=int, default=16, help="moe_experts: experts of the layer")
+    k.add_argument("--gated", action="store_true", help="moe_experts: experts of the form down(silu(gate x) * up x)")
     k.add_argument("--top", type=int, default=4, help="moe_experts: experts a row chooses")
     k.add_argument("--iters", type=int, default=50)
     k.add_argument("--warmup", type=int, default=5)

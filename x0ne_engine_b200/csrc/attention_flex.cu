@@ -2,7 +2,8 @@
 // not take: keys and values of different widths (any width: rows are padded with zeros to a
 // multiple of 16 in shared memory), values that are the leading part of the key rows (a latent
 // cache read by every head), a chunked mask, a sliding window, first keys that stay visible whatever
-// the window, a per-head sink in the softmax denominator and a per-(row, head) sigmoid gate on the output.
+// the window, a per-head sink in the softmax denominator, a per-head slope times the distance i - j taken off the
+// scaled score, and a sigmoid gate on the output per (row, head) or per (row, head, value).
 //
 // Both kernels are flash attention on `mma.sync` m16n8k16 with float32 accumulation.  Scores,
 // maxima, sums and weights are float32; for the product with the values a weight p is split into
@@ -211,6 +212,8 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
     const int pos0 = seq_pos0[seq] + (row0 - seq_first_row[seq]);
     const int n_rows = min(FX_TILE_ROWS, seq_first_row[seq + 1] - row0);
     const float sink2 = ex.sink != nullptr ? ex.sink[head] * FX_LOG2E : -INFINITY;
+    const bool sloped = ex.slope != nullptr;
+    const float sl2 = sloped ? ex.slope[head] * FX_LOG2E : 0.f;       // taken off per position of distance, in the exp2 domain
     pdl_wait();
     const int64_t q_ld = ex.q_ld > 0 ? ex.q_ld : (int64_t)q_heads * sh.dk;
     const bf16* safe = (const bf16*)cache.base;
@@ -278,6 +281,14 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
             for (int n = 0; n < 8; ++n) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[n][e] *= sc2;
+                if (sloped) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int j = j0 + 8 * n + 2 * t + e;
+                        s[n][e] -= sl2 * (float)(pos_a - j);
+                        s[n][2 + e] -= sl2 * (float)(pos_b - j);
+                    }
+                }
                 mx_a = fmaxf(mx_a, fmaxf(s[n][0], s[n][1]));
                 mx_b = fmaxf(mx_b, fmaxf(s[n][2], s[n][3]));
             }
@@ -287,8 +298,13 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int j = j0 + 8 * n + 2 * t + e;
-                    s[n][e] = (ok_a && j <= pos_a && (j >= lo_a || j < ex.keep_first)) ? s[n][e] * sc2 : -INFINITY;
-                    s[n][2 + e] = (ok_b && j <= pos_b && (j >= lo_b || j < ex.keep_first)) ? s[n][2 + e] * sc2 : -INFINITY;
+                    float sa = s[n][e] * sc2, sb = s[n][2 + e] * sc2;
+                    if (sloped) {
+                        sa -= sl2 * (float)(pos_a - j);
+                        sb -= sl2 * (float)(pos_b - j);
+                    }
+                    s[n][e] = (ok_a && j <= pos_a && (j >= lo_a || j < ex.keep_first)) ? sa : -INFINITY;
+                    s[n][2 + e] = (ok_b && j <= pos_b && (j >= lo_b || j < ex.keep_first)) ? sb : -INFINITY;
                     mx_a = fmaxf(mx_a, s[n][e]);
                     mx_b = fmaxf(mx_b, s[n][2 + e]);
                 }
@@ -332,11 +348,14 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
     }
     f_a *= l_a > 0.f ? 1.0f / l_a : 0.f;
     f_b *= l_b > 0.f ? 1.0f / l_b : 0.f;
-    if (ex.gate != nullptr) {
+    const bool wide = ex.gate != nullptr && ex.gate_wide > 0;       // a gate per value of the head, not one per head
+    if (ex.gate != nullptr && !wide) {
         const bf16* gt = (const bf16*)ex.gate;
         if (ok_a) f_a *= 1.0f / (1.0f + expf(-__bfloat162float(gt[(int64_t)(row0 + r_a) * ex.gate_ld + head])));
         if (ok_b) f_b *= 1.0f / (1.0f + expf(-__bfloat162float(gt[(int64_t)(row0 + r_b) * ex.gate_ld + head])));
     }
+    const bf16* ga = (const bf16*)ex.gate + (int64_t)(row0 + r_a) * ex.gate_ld + (int64_t)head * sh.vd;
+    const bf16* gb = (const bf16*)ex.gate + (int64_t)(row0 + r_b) * ex.gate_ld + (int64_t)head * sh.vd;
     bf16* oa = out + ((int64_t)(row0 + r_a) * q_heads + head) * sh.vd;
     bf16* ob = out + ((int64_t)(row0 + r_b) * q_heads + head) * sh.vd;
 #pragma unroll
@@ -345,8 +364,13 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
         for (int e = 0; e < 2; ++e) {
             const int c = 8 * n + 2 * t + e;
             if (c < sh.vd) {
-                if (ok_a) oa[c] = __float2bfloat16_rn(o[n][e] * f_a);
-                if (ok_b) ob[c] = __float2bfloat16_rn(o[n][2 + e] * f_b);
+                if (wide) {
+                    if (ok_a) oa[c] = __float2bfloat16_rn(o[n][e] * f_a * (1.0f / (1.0f + expf(-__bfloat162float(ga[c])))));
+                    if (ok_b) ob[c] = __float2bfloat16_rn(o[n][2 + e] * f_b * (1.0f / (1.0f + expf(-__bfloat162float(gb[c])))));
+                } else {
+                    if (ok_a) oa[c] = __float2bfloat16_rn(o[n][e] * f_a);
+                    if (ok_b) ob[c] = __float2bfloat16_rn(o[n][2 + e] * f_b);
+                }
             }
         }
     }
@@ -382,6 +406,10 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
     fx_load_rows_async(qs, sh.ks, q + (int64_t)row * q_ld + (int64_t)head0 * sh.dk, sh.dk, 16, 0, n_items - 1, sh.dk, sh.dkp, tid, 128, safe, pk);
 
     const float sc2 = scale * FX_LOG2E;
+    // the distance slopes of this thread's two items (q heads head0 + g and head0 + g + 8), in the exp2 domain
+    const bool sloped = ex.slope != nullptr;
+    const float sl_a = sloped && g < n_items ? ex.slope[head0 + g] * FX_LOG2E : 0.f;
+    const float sl_b = sloped && g + 8 < n_items ? ex.slope[head0 + g + 8] * FX_LOG2E : 0.f;
     const int key_lo = fx_first_key(pos, window, ex.chunk);
     const int pg_lo = key_lo / FX_PAGE, pg_hi = slot >= 0 ? pos / FX_PAGE : pg_lo - 1;
     // the walk: pages of kept first keys that lie wholly before the window's first page, then the window's pages
@@ -438,8 +466,13 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
             for (int e = 0; e < 2; ++e) {
                 const int j = jw + 8 * n + 2 * t + e;
                 const bool vis = j <= pos && (j >= key_lo || j < ex.keep_first);
-                s[n][e] = vis ? s[n][e] * sc2 : -INFINITY;
-                s[n][2 + e] = vis ? s[n][2 + e] * sc2 : -INFINITY;
+                float sa = s[n][e] * sc2, sb = s[n][2 + e] * sc2;
+                if (sloped) {
+                    sa -= sl_a * (float)(pos - j);
+                    sb -= sl_b * (float)(pos - j);
+                }
+                s[n][e] = vis ? sa : -INFINITY;
+                s[n][2 + e] = vis ? sb : -INFINITY;
             }
         }
         float mx_a = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
@@ -517,12 +550,16 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
         ll = ll * fin + exp2f(sink2 - mf);
     }
     fin *= ll > 0.f ? 1.0f / ll : 0.f;
-    if (ex.gate != nullptr) fin *= 1.0f / (1.0f + expf(-__bfloat162float(((const bf16*)ex.gate)[(int64_t)row * ex.gate_ld + head])));
+    const bool wide = ex.gate != nullptr && ex.gate_wide > 0;
+    if (ex.gate != nullptr && !wide) fin *= 1.0f / (1.0f + expf(-__bfloat162float(((const bf16*)ex.gate)[(int64_t)row * ex.gate_ld + head])));
+    const bf16* gw = (const bf16*)ex.gate + (int64_t)row * ex.gate_ld + (int64_t)head * sh.vd;
     bf16* orow = out + ((int64_t)row * q_heads + head) * sh.vd;
     for (int c = c0; c < sh.vd; c += 8) {
         float acc = 0.f;
         for (int w = 0; w < 4; ++w) acc += mg[((int64_t)w * 16 + item) * ps + 2 + c] * f[w];
-        orow[c] = __float2bfloat16_rn(acc * fin);
+        acc *= fin;
+        if (wide) acc *= 1.0f / (1.0f + expf(-__bfloat162float(gw[c])));
+        orow[c] = __float2bfloat16_rn(acc);
     }
 }
 
@@ -565,7 +602,8 @@ flex_decode_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ o
                 ll = ll * fin + exp2f(sink2 - mf);
             }
             fin *= ll > 0.f ? 1.0f / ll : 0.f;
-            if (ex.gate != nullptr) fin *= 1.0f / (1.0f + expf(-__bfloat162float(((const bf16*)ex.gate)[(int64_t)row * ex.gate_ld + head])));
+            if (ex.gate != nullptr && ex.gate_wide <= 0)
+                fin *= 1.0f / (1.0f + expf(-__bfloat162float(((const bf16*)ex.gate)[(int64_t)row * ex.gate_ld + head])));
             fin_s[item] = fin;
         }
     }
@@ -576,7 +614,10 @@ flex_decode_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ o
         const float* src = base + (int64_t)item * ps + 2 + c;
         float acc = 0.f;
         for (int s = 0; s < splits; ++s) acc += src[s * step] * wgt[item][s];
-        orow[i] = __float2bfloat16_rn(acc * fin_s[item]);
+        acc *= fin_s[item];
+        if (ex.gate != nullptr && ex.gate_wide > 0)      // heads head0 .. of the row lie one after the other: value i of them
+            acc *= 1.0f / (1.0f + expf(-__bfloat162float(((const bf16*)ex.gate)[(int64_t)row * ex.gate_ld + (int64_t)head0 * vd + i])));
+        orow[i] = __float2bfloat16_rn(acc);
     }
 }
 

@@ -190,7 +190,7 @@ __global__ void moe_group_kernel(const int32_t* __restrict__ chosen, int pairs, 
 template <typename T, int ACT>
 __global__ void __launch_bounds__(256) moe_product_kernel(const T* __restrict__ a, int64_t lda, const T* __restrict__ w, int N, int K,
                                                           const int32_t* __restrict__ listed, const int32_t* __restrict__ tiles,
-                                                          int top, void* __restrict__ out) {
+                                                          int top, void* __restrict__ out, int pair_block) {
     __shared__ float As[16][MOE_TILE_M + 4];
     __shared__ float Ws[16][64 + 4];
     __shared__ float Us[ACT == 2 ? 16 : 1][64 + 4];
@@ -221,8 +221,15 @@ __global__ void __launch_bounds__(256) moe_product_kernel(const T* __restrict__ 
             const int idx = tid + it * 256;
             const int r = idx / 16, kk = idx % 16;
             const int gn = n0 + r, gk = k0 + kk;
-            Ws[kk][r] = (gn < N && gk < K) ? to_f32(we[(int64_t)gn * K + gk]) : 0.f;
-            if (ACT == 2) Us[kk][r] = (gn < N && gk < K) ? to_f32(we[(int64_t)(N + gn) * K + gk]) : 0.f;
+            if (ACT == 2) {
+                // gate row gn and its up row: all gate rows then all up rows, or blocks of pair_block gate rows and their up rows
+                const int64_t gr = pair_block > 0 ? (int64_t)(gn / pair_block) * 2 * pair_block + gn % pair_block : gn;
+                const int64_t ur = gr + (pair_block > 0 ? pair_block : N);
+                Ws[kk][r] = (gn < N && gk < K) ? to_f32(we[gr * K + gk]) : 0.f;
+                Us[kk][r] = (gn < N && gk < K) ? to_f32(we[ur * K + gk]) : 0.f;
+            } else {
+                Ws[kk][r] = (gn < N && gk < K) ? to_f32(we[(int64_t)gn * K + gk]) : 0.f;
+            }
         }
         __syncthreads();
 #pragma unroll
@@ -387,22 +394,23 @@ X0NE_API int x0ne_moe_group(const int32_t* chosen, int pairs, int experts, int32
 
 // which = 0: up product with the squared ReLU (a: the rows [*, K], out: activation type [pairs][N]);
 // which = 1: down product (a: the activations [pairs][K], out: float32 [pairs][N]).  w: [experts][N][K].
-// which = 2: gated up product, silu(gate) * up (w: [experts][2 N][K], an expert's gate rows before its up rows).
+// which = 2: gated up product, silu(gate) * up (w: [experts][2 N][K], an expert's gate rows before its up rows, or, with
+// pair_block > 0 (which divides N), in blocks of pair_block gate rows followed by the up rows of the same outputs).
 X0NE_API int x0ne_moe_product(int which, const void* a, int64_t lda, const void* w, int dt, int N, int K, const int32_t* listed,
-                              const int32_t* tiles, int max_tiles, int top, void* out, cudaStream_t stream) {
+                              const int32_t* tiles, int max_tiles, int top, void* out, int pair_block, cudaStream_t stream) {
     X0NE_REQUIRE((which == 0 || which == 1 || which == 2) && N > 0 && K > 0 && lda >= K && top > 0 && max_tiles >= 0, "moe_product: N %d K %d lda %lld", N, K, (long long)lda);
     X0NE_REQUIRE(dt == X0NE_F32 || dt == X0NE_BF16, "moe_product: unknown dtype tag %d", dt);
     if (max_tiles == 0) return 0;
     X0NE_REQUIRE(max_tiles <= 65535, "moe_product: %d tiles in one launch", max_tiles);
     const dim3 grid((N + 63) / 64, max_tiles), block(256);
     if (dt == X0NE_F32) {
-        if (which == 0) x0ne_launch(moe_product_kernel<float, 1>, grid, block, 0, stream, (const float*)a, lda, (const float*)w, N, K, listed, tiles, top, out);
-        else if (which == 2) x0ne_launch(moe_product_kernel<float, 2>, grid, block, 0, stream, (const float*)a, lda, (const float*)w, N, K, listed, tiles, top, out);
-        else x0ne_launch(moe_product_kernel<float, 0>, grid, block, 0, stream, (const float*)a, lda, (const float*)w, N, K, listed, tiles, top, out);
+        if (which == 0) x0ne_launch(moe_product_kernel<float, 1>, grid, block, 0, stream, (const float*)a, lda, (const float*)w, N, K, listed, tiles, top, out, pair_block);
+        else if (which == 2) x0ne_launch(moe_product_kernel<float, 2>, grid, block, 0, stream, (const float*)a, lda, (const float*)w, N, K, listed, tiles, top, out, pair_block);
+        else x0ne_launch(moe_product_kernel<float, 0>, grid, block, 0, stream, (const float*)a, lda, (const float*)w, N, K, listed, tiles, top, out, pair_block);
     } else {
-        if (which == 0) x0ne_launch(moe_product_kernel<bf16, 1>, grid, block, 0, stream, (const bf16*)a, lda, (const bf16*)w, N, K, listed, tiles, top, out);
-        else if (which == 2) x0ne_launch(moe_product_kernel<bf16, 2>, grid, block, 0, stream, (const bf16*)a, lda, (const bf16*)w, N, K, listed, tiles, top, out);
-        else x0ne_launch(moe_product_kernel<bf16, 0>, grid, block, 0, stream, (const bf16*)a, lda, (const bf16*)w, N, K, listed, tiles, top, out);
+        if (which == 0) x0ne_launch(moe_product_kernel<bf16, 1>, grid, block, 0, stream, (const bf16*)a, lda, (const bf16*)w, N, K, listed, tiles, top, out, pair_block);
+        else if (which == 2) x0ne_launch(moe_product_kernel<bf16, 2>, grid, block, 0, stream, (const bf16*)a, lda, (const bf16*)w, N, K, listed, tiles, top, out, pair_block);
+        else x0ne_launch(moe_product_kernel<bf16, 0>, grid, block, 0, stream, (const bf16*)a, lda, (const bf16*)w, N, K, listed, tiles, top, out, pair_block);
     }
     X0NE_LAUNCH_CHECK();
 }

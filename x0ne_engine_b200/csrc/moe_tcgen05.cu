@@ -7,6 +7,9 @@
 //         [experts x N][K]; the epilogue writes relu(.)^2 as bfloat16 to act[place][N]
 //   down: A = act [places][K], W = down weights [experts x N][K]; the epilogue writes float32 to
 //         y[pair][N], the pair looked up from the list (a row of the tile is one thread's)
+//   gated up: W = [experts x N][K] with N = 2 x the experts' inner width, an expert's rows in blocks of 256: 128 gate
+//         rows, then the 128 up rows of the same outputs; a tile's accumulator then holds a gate value and its up value
+//         128 columns apart, and the epilogue writes silu(gate) * up as bfloat16 to act[place][N / 2]
 //
 // The pipeline is the one of gemm_tcgen05.cu: a copy thread (TMA, 128-byte swizzle, 4 stages), an MMA
 // thread (accumulator double-buffered in tensor memory) and four epilogue warps; blocks are
@@ -33,7 +36,11 @@ struct MtShared {
     int failed;
 };
 
-template <bool UP>
+#define MT_UP 0
+#define MT_DOWN 1
+#define MT_GATED 2
+
+template <int MODE>
 __global__ void __launch_bounds__(MT_THREADS) moe_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                             const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
                                                             int N, int K, const int32_t* __restrict__ listed,
@@ -133,13 +140,36 @@ __global__ void __launch_bounds__(MT_THREADS) moe_tc_kernel(const __grid_constan
             const int first = tiles[3 * mt + 1], count = tiles[3 * mt + 2];
             const int r = quarter * 32 + lane;
             int64_t row = -1;                              // the output row of this thread, or none
-            if (r < count) row = UP ? (int64_t)(first + r) : (int64_t)listed[first + r];
+            if (r < count) row = MODE != MT_DOWN ? (int64_t)(first + r) : (int64_t)listed[first + r];
             if (!mbar_wait(&sh->accum_full[ab], (t >> 1) & 1, status, 3) || sh->failed) {
                 sh->failed = 1;
                 break;
             }
             tc_fence_after();
             const uint32_t trow = tmem + ab * 256 + ((uint32_t)(quarter * 32) << 16);
+            if (MODE == MT_GATED) {
+                // columns c and 128 + c of the tile are the gate and the up value of output n0 / 2 + c (N is a multiple of 256)
+                const int half = N / 2;
+#pragma unroll 1
+                for (int c = 0; c < MT_BN / 64; ++c) {
+                    float v[32], u[32];
+                    tc_ld32(trow + c * 32, v);
+                    tc_ld32(trow + MT_BN / 2 + c * 32, u);
+                    if (row < 0) continue;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + __expf(-v[i])) * u[i];
+                    bf16* dst = (bf16*)out + row * half + n0 / 2 + c * 32;
+                    if ((((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) tc_store8(dst + i, v + i);
+                    } else {
+                        for (int i = 0; i < 32; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(&sh->accum_empty[ab]);
+                continue;
+            }
 #pragma unroll 1
             for (int c = 0; c < MT_BN / 32; ++c) {
                 const int n = n0 + c * 32;
@@ -147,7 +177,7 @@ __global__ void __launch_bounds__(MT_THREADS) moe_tc_kernel(const __grid_constan
                 float v[32];
                 tc_ld32(trow + c * 32, v);
                 if (row < 0) continue;
-                if (UP) {
+                if (MODE == MT_UP) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const float x = fmaxf(v[i], 0.f);
@@ -211,13 +241,15 @@ X0NE_API int x0ne_moe_gather_rows(const void* x, int K, const int32_t* listed, c
 }
 
 // which 0: up (a: gathered rows [a_rows][K], out: bfloat16 act [places][N]); which 1: down (a: act [a_rows][K], out:
-// float32 y [pairs][N]).  w: [experts][N][K] bfloat16.  tiles: [max_tiles][3] from the grouping kernel run with
+// float32 y [pairs][N]); which 2: gated up (a as for 0, w rows in blocks of 128 gate and 128 up rows, N a multiple of 256,
+// out: bfloat16 act [places][N / 2]).  w: [experts][N][K] bfloat16.  tiles: [max_tiles][3] from the grouping kernel run with
 // tiles of 128 pairs; n_real: how many of them are real (device memory).
 X0NE_API int x0ne_moe_product_tc(int which, const void* a, int64_t a_rows, const void* w, int experts, int N, int K,
                                  const int32_t* listed, const int32_t* tiles, const int32_t* n_real, int max_tiles, void* out,
                                  int* status, cudaStream_t stream) {
-    X0NE_REQUIRE((which == 0 || which == 1) && experts > 0 && N > 0 && K > 0 && K % 8 == 0 && a_rows > 0 && max_tiles >= 0,
+    X0NE_REQUIRE((which == 0 || which == 1 || which == 2) && experts > 0 && N > 0 && K > 0 && K % 8 == 0 && a_rows > 0 && max_tiles >= 0,
                  "moe_product_tc: experts %d N %d K %d (K must be a multiple of 8)", experts, N, K);
+    X0NE_REQUIRE(which != 2 || N % MT_BN == 0, "moe_product_tc: gated experts of %d rows (blocks of %d)", N, MT_BN);
     X0NE_REQUIRE(status != nullptr && n_real != nullptr, "moe_product_tc: no status word or no tile count");
     X0NE_REQUIRE((((uintptr_t)a | (uintptr_t)w) & 15) == 0, "moe_product_tc: operands are not 16-byte aligned");
     if (max_tiles == 0) return 0;
@@ -227,11 +259,12 @@ X0NE_API int x0ne_moe_product_tc(int which, const void* a, int64_t a_rows, const
     const size_t smem = (size_t)MT_STAGES * (MT_BM * 128 + MT_BN * 128) + sizeof(MtShared) + 1024;
     static OncePerDevice configured;
     if (configured.need()) {
-        cudaError_t e1 = cudaFuncSetAttribute(moe_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaError_t e2 = cudaFuncSetAttribute(moe_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e1 != cudaSuccess || e2 != cudaSuccess) {
+        cudaError_t e1 = cudaFuncSetAttribute(moe_tc_kernel<MT_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e2 = cudaFuncSetAttribute(moe_tc_kernel<MT_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e3 = cudaFuncSetAttribute(moe_tc_kernel<MT_GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess) {
             x0ne_set_error("moe_product_tc: cannot set %zu bytes of shared memory", smem);
-            return (int)(e1 != cudaSuccess ? e1 : e2);
+            return (int)(e1 != cudaSuccess ? e1 : (e2 != cudaSuccess ? e2 : e3));
         }
         configured.done();
     }
@@ -247,8 +280,10 @@ X0NE_API int x0ne_moe_product_tc(int which, const void* a, int64_t a_rows, const
     // rows gave other logits than the same launches made one by one (which leave more time between the two kernels); with a
     // plain launch and the proxy fence in the kernel they give the same bits.  The kernel still lets its own successor start early.
     if (which == 0)
-        moe_tc_kernel<true><<<grid, MT_THREADS, smem, stream>>>(map_a, map_w, out, N, K, listed, tiles, n_real, max_tiles, n_tiles_n, status);
+        moe_tc_kernel<MT_UP><<<grid, MT_THREADS, smem, stream>>>(map_a, map_w, out, N, K, listed, tiles, n_real, max_tiles, n_tiles_n, status);
+    else if (which == 2)
+        moe_tc_kernel<MT_GATED><<<grid, MT_THREADS, smem, stream>>>(map_a, map_w, out, N, K, listed, tiles, n_real, max_tiles, n_tiles_n, status);
     else
-        moe_tc_kernel<false><<<grid, MT_THREADS, smem, stream>>>(map_a, map_w, out, N, K, listed, tiles, n_real, max_tiles, n_tiles_n, status);
+        moe_tc_kernel<MT_DOWN><<<grid, MT_THREADS, smem, stream>>>(map_a, map_w, out, N, K, listed, tiles, n_real, max_tiles, n_tiles_n, status);
     X0NE_LAUNCH_CHECK();
 }

@@ -97,7 +97,7 @@ _SIGNATURES = {
     "x0ne_moe_group": [_P, _I, _I, _P, _P, _P, _I, _I, _P, _P],
     "x0ne_moe_gather_rows": [_P, _I, _P, _P, _I, _I, _P, _I, _P],
     "x0ne_moe_product_tc": [_I, _P, _L, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P],
-    "x0ne_moe_product": [_I, _P, _L, _P, _I, _I, _I, _P, _P, _I, _I, _P, _P],
+    "x0ne_moe_product": [_I, _P, _L, _P, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P],
     "x0ne_moe_combine": [_P, _P, _I, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P],
     "x0ne_add_rmsnorm": [_P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
     "x0ne_add2_rmsnorm": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
@@ -403,13 +403,17 @@ def moe_gather_rows(x: torch.Tensor, listed: torch.Tensor, offsets: torch.Tensor
 def moe_product_tc(which: int, a: torch.Tensor, w: torch.Tensor, listed: torch.Tensor, tiles: torch.Tensor,
                    n_real: torch.Tensor, max_tiles: int, out: torch.Tensor) -> None:
     """The experts' products on tcgen05 over tiles of 128 listed pairs (moe_tcgen05.cu).  which 0: a = the gathered rows
-    [places, K], out = relu(.)^2 as bfloat16 [places, N]; which 1: a = those activations, out = float32 [pairs, N] by pair."""
+    [places, K], out = relu(.)^2 as bfloat16 [places, N]; which 1: a = those activations, out = float32 [pairs, N] by pair;
+    which 2: a as for 0, w [experts, 2 N, K] in blocks of MOE_PAIR_BLOCK gate rows and their up rows, out = silu(gate) * up
+    as bfloat16 [places, N]."""
     global tc_used
     lib = _lib("tc")
     _need(a, torch.bfloat16, "expert input")
     _need(w, torch.bfloat16, "expert weights")
     _need(out, torch.float32 if which == 1 else torch.bfloat16, "expert output")
-    if w.dim() != 3 or a.shape[-1] != w.shape[2] or out.shape[-1] != w.shape[1] or tiles.numel() < 3 * max_tiles:
+    n_out = w.shape[1] // 2 if which == 2 else w.shape[1]
+    if w.dim() != 3 or a.shape[-1] != w.shape[2] or out.shape[-1] != n_out or tiles.numel() < 3 * max_tiles \
+            or (which == 2 and w.shape[1] % (2 * MOE_PAIR_BLOCK)):
         raise KernelError("moe_product_tc: shapes do not match")
     tc_used = True
     _check(lib, lib.x0ne_moe_product_tc(which, _ptr(a), a.numel() // a.shape[-1], _ptr(w), w.shape[0], w.shape[1], w.shape[2],
@@ -417,11 +421,15 @@ def moe_product_tc(which: int, a: torch.Tensor, w: torch.Tensor, listed: torch.T
                                         _ptr(gemm_tc_status(a.device)), _stream()), "moe_product_tc")
 
 
+MOE_PAIR_BLOCK = 128       # gated experts whose inner width is a multiple of this keep gate and up rows in blocks of it
+
+
 def moe_product(which: int, a: torch.Tensor, w: torch.Tensor, listed: torch.Tensor, tiles: torch.Tensor, n_tiles: int, top: int,
-                out: torch.Tensor) -> None:
+                out: torch.Tensor, pair_block: int = 0) -> None:
     """The experts' products over the first n_tiles tiles.  which 0: out[pair] = relu(x[pair // top] W_e^T)^2 in the
     activation type; which 1: out[pair] = act[pair] W_e^T in float32.  w is [experts, N, K].  which 2: out[pair] =
-    silu(x W_gate_e^T) * (x W_up_e^T) with w [experts, 2 N, K], an expert's gate rows before its up rows."""
+    silu(x W_gate_e^T) * (x W_up_e^T) with w [experts, 2 N, K], an expert's gate rows before its up rows, or, with
+    `pair_block`, in blocks of that many gate rows followed by the up rows of the same outputs."""
     _need(a, w.dtype, "expert input")
     _need(w, w.dtype, "expert weights")
     _need(out, torch.float32 if which == 1 else w.dtype, "expert output")
@@ -430,9 +438,11 @@ def moe_product(which: int, a: torch.Tensor, w: torch.Tensor, listed: torch.Tens
     n, k = (w.shape[1] // 2 if which == 2 else w.shape[1]), w.shape[2]
     if w.dim() != 3 or a.shape[-1] != k or out.shape[-1] != n or tiles.numel() < 3 * n_tiles or (which == 2 and w.shape[1] % 2):
         raise KernelError("moe_product: shapes do not match")
+    if which == 2 and pair_block and n % pair_block:
+        raise KernelError(f"moe_product: {n} outputs do not split into blocks of {pair_block}")
     lib = _lib("core")
     _check(lib, lib.x0ne_moe_product(which, _ptr(a), a.shape[-1], _ptr(w), dtype_tag(w.dtype), n, k, _ptr(listed), _ptr(tiles),
-                                     n_tiles, top, _ptr(out), _stream()), "moe_product")
+                                     n_tiles, top, _ptr(out), int(pair_block) if which == 2 else 0, _stream()), "moe_product")
 
 
 def moe_combine(y: torch.Tensor, x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, top: int, experts: int,

@@ -13,7 +13,7 @@
 //
 // The state of a sequence is one float32 array: heads x N x N, then `width` values of the last h.  State, decays
 // and every sum are float32; r, k, v, the gate and h come in the activation type.  A sequence's result depends
-// on its own rows and state only, and every sum runs over i ascending, so it is the same bits however the
+// on its own rows and state only, and every sum runs in one fixed order, so it is the same bits however the
 // sequence's tokens are cut into passes and whatever else is in a pass.
 #include "common.cuh"
 
@@ -42,23 +42,32 @@ __global__ void token_shift_mix_kernel(const T* __restrict__ h, const float* __r
 }
 
 // ----------------------------------------------------------------------------------------
-// scan: one block per (sequence, head); thread j owns column j of S (N values in registers)
+// scan: one block per (sequence, head); WKV_P threads share column j of S, each with NB / WKV_P of its N values in
+// registers (key channels 4 (e WKV_P + p) + 0..3 for e = 0, 1, ...), so a token costs each thread NB / WKV_P steps of
+// the recurrence, four partial sums that do not wait on each other, and two shuffles.  The rows of the next 16 tokens
+// are fetched into registers while the current 16 are worked on out of shared memory.
 // ----------------------------------------------------------------------------------------
 #define WKV_TB 16      // tokens staged in shared memory at a time
+#define WKV_P 4        // threads per column of the state
 
 template <typename T, int NB>
-__global__ void __launch_bounds__(NB) wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
-                                                     const float* __restrict__ z, const float* __restrict__ w0,
-                                                     const float* __restrict__ u, const T* __restrict__ h,
-                                                     float* __restrict__ o, float* __restrict__ state, int64_t state_stride,
-                                                     const int32_t* __restrict__ seq_first_row, const int32_t* __restrict__ seq_slot,
-                                                     int heads, int N, int width) {
+__global__ void __launch_bounds__(NB * WKV_P) wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
+                                                             const float* __restrict__ z, const float* __restrict__ w0,
+                                                             const float* __restrict__ u, const T* __restrict__ h,
+                                                             float* __restrict__ o, float* __restrict__ state, int64_t state_stride,
+                                                             const int32_t* __restrict__ seq_first_row, const int32_t* __restrict__ seq_slot,
+                                                             int heads, int N, int width) {
+    constexpr int NT = NB * WKV_P;              // threads
+    constexpr int PER = NB / WKV_P;             // state values per thread
+    constexpr int FETCH = WKV_TB * NB / NT;     // values of each staged array a thread fetches per 16 tokens
+    static_assert(PER % 4 == 0 && WKV_TB * NB % NT == 0, "the column split must leave groups of four key channels");
     __shared__ __align__(16) float rs[WKV_TB][NB], ks[WKV_TB][NB], ws[WKV_TB][NB], vs[WKV_TB][NB];
     __shared__ __align__(16) float us[NB], w0s[NB];
     pdl_launch_dependents();
-    const int seq = blockIdx.x, head = blockIdx.y, j = threadIdx.x;
+    const int seq = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+    const int j = tid / WKV_P, p = tid % WKV_P;
     const int64_t ld = (int64_t)heads * N;
-    for (int i = j; i < NB; i += NB) {
+    for (int i = tid; i < NB; i += NT) {
         us[i] = i < N ? u[head * N + i] : 0.f;
         w0s[i] = i < N ? w0[head * N + i] : 0.f;
     }
@@ -67,50 +76,78 @@ __global__ void __launch_bounds__(NB) wkv_scan_kernel(const T* __restrict__ r, c
     const int row0 = seq_first_row[seq], row1 = seq_first_row[seq + 1];
     if (slot < 0 || row1 <= row0) return;
     float* S = state + (int64_t)slot * state_stride + (int64_t)head * N * N;
-    float s[NB];
+    float s[PER];
 #pragma unroll
-    for (int i = 0; i < NB; ++i) s[i] = (i < N && j < N) ? S[(int64_t)i * N + j] : 0.f;
+    for (int e = 0; e < PER / 4; ++e)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int i = 4 * (e * WKV_P + p) + q;
+            s[4 * e + q] = (i < N && j < N) ? S[(int64_t)i * N + j] : 0.f;
+        }
+    float fr[FETCH], fk[FETCH], fv[FETCH], fz[FETCH];
+    auto fetch = [&](int t0) {
+#pragma unroll
+        for (int x = 0; x < FETCH; ++x) {
+            const int e = tid + x * NT, t = e / NB, i = e % NB;
+            const bool in = i < N && t0 + t < row1;
+            const int64_t at = (int64_t)(t0 + t) * ld + (int64_t)head * N + i;
+            fr[x] = in ? to_f32(r[at]) : 0.f;
+            fk[x] = in ? to_f32(k[at]) : 0.f;
+            fv[x] = in ? to_f32(v[at]) : 0.f;
+            fz[x] = in ? z[at] : 0.f;
+        }
+    };
+    fetch(row0);
+    __syncthreads();                            // us, w0s
     for (int t0 = row0; t0 < row1; t0 += WKV_TB) {
         const int nt = min(WKV_TB, row1 - t0);
-        __syncthreads();
-        for (int e = j; e < nt * NB; e += NB) {
-            const int t = e / NB, i = e % NB;
-            const int64_t at = (int64_t)(t0 + t) * ld + (int64_t)head * N + i;
-            const bool in = i < N;
-            rs[t][i] = in ? to_f32(r[at]) : 0.f;
-            ks[t][i] = in ? to_f32(k[at]) : 0.f;
-            vs[t][i] = in ? to_f32(v[at]) : 0.f;
-            ws[t][i] = in ? expf(-expf(z[at] + w0s[i])) : 0.f;
+#pragma unroll
+        for (int x = 0; x < FETCH; ++x) {
+            const int e = tid + x * NT, t = e / NB, i = e % NB;
+            rs[t][i] = fr[x];
+            ks[t][i] = fk[x];
+            vs[t][i] = fv[x];
+            ws[t][i] = i < N ? expf(-expf(fz[x] + w0s[i])) : 0.f;
         }
         __syncthreads();
+        if (t0 + WKV_TB < row1) fetch(t0 + WKV_TB);
         for (int t = 0; t < nt; ++t) {
             const float vj = vs[t][j];
-            float acc = 0.f;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < NB; i += 4) {
-                const float4 r4 = *reinterpret_cast<const float4*>(&rs[t][i]);
-                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][i]);
-                const float4 w4 = *reinterpret_cast<const float4*>(&ws[t][i]);
-                const float4 u4 = *reinterpret_cast<const float4*>(&us[i]);
+            for (int e = 0; e < PER / 4; ++e) {
+                const int i0 = 4 * (e * WKV_P + p);
+                const float4 r4 = *reinterpret_cast<const float4*>(&rs[t][i0]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][i0]);
+                const float4 w4 = *reinterpret_cast<const float4*>(&ws[t][i0]);
+                const float4 u4 = *reinterpret_cast<const float4*>(&us[i0]);
                 const float rr[4] = {r4.x, r4.y, r4.z, r4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w};
                 const float ww[4] = {w4.x, w4.y, w4.z, w4.w}, uu[4] = {u4.x, u4.y, u4.z, u4.w};
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float kv = kk[e] * vj;
-                    acc = fmaf(rr[e], fmaf(uu[e], kv, s[i + e]), acc);
-                    s[i + e] = fmaf(ww[e], s[i + e], kv);
+                for (int q = 0; q < 4; ++q) {
+                    const float kv = kk[q] * vj;
+                    acc[q] = fmaf(rr[q], fmaf(uu[q], kv, s[4 * e + q]), acc[q]);
+                    s[4 * e + q] = fmaf(ww[q], s[4 * e + q], kv);
                 }
             }
-            if (j < N) o[(int64_t)(t0 + t) * ld + (int64_t)head * N + j] = acc;
+            float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+            for (int off = 1; off < WKV_P; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            if (p == 0 && j < N) o[(int64_t)(t0 + t) * ld + (int64_t)head * N + j] = sum;
         }
+        __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < NB; ++i)
-        if (i < N && j < N) S[(int64_t)i * N + j] = s[i];
+    for (int e = 0; e < PER / 4; ++e)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int i = 4 * (e * WKV_P + p) + q;
+            if (i < N && j < N) S[(int64_t)i * N + j] = s[4 * e + q];
+        }
     if (head == 0) {        // the last row's h, for the token shift of the sequence's next token
         float* last = state + (int64_t)slot * state_stride + (int64_t)heads * N * N;
         const T* hr = h + (int64_t)(row1 - 1) * width;
-        for (int c = j; c < width; c += NB) last[c] = to_f32(hr[c]);
+        for (int c = tid; c < width; c += NT) last[c] = to_f32(hr[c]);
     }
 }
 
@@ -205,7 +242,7 @@ static int wkv_scan_launch(const T* r, const T* k, const T* v, const float* z, c
                            float* state, int64_t state_stride, const int32_t* seq_first_row, const int32_t* seq_slot, int n_seqs,
                            int heads, int N, int width, cudaStream_t stream) {
     const dim3 grid(n_seqs, heads);
-#define WKV_SCAN(NB) x0ne_launch(wkv_scan_kernel<T, NB>, grid, dim3(NB), 0, stream, r, k, v, z, w0, u, h, o, state, state_stride, seq_first_row, seq_slot, heads, N, width)
+#define WKV_SCAN(NB) x0ne_launch(wkv_scan_kernel<T, NB>, grid, dim3(NB * WKV_P), 0, stream, r, k, v, z, w0, u, h, o, state, state_stride, seq_first_row, seq_slot, heads, N, width)
     if (N <= 32) WKV_SCAN(32);
     else if (N <= 64) WKV_SCAN(64);
     else if (N <= 96) WKV_SCAN(96);

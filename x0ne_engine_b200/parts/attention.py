@@ -70,7 +70,7 @@ def run_attention_ex(ctx, q, out, view, n_rows, q_heads, scale, window, extra):
     """Attention with what `extra` asks for (`ops.attn_extra`: chunked mask, values out of the keys,
     sink, gate, queries inside a wider buffer): the general bfloat16 kernels where they take the
     shape, else the plain kernel (which is also the whole 32-bit path)."""
-    if not ops.attention_flex_takes(view, q.dtype, extra.v_from_k, ctx.decode) or extra.slope or extra.gate_wide:
+    if not ops.attention_flex_takes(view, q.dtype, extra.v_from_k, ctx.decode):
         ops.attention_rows(q, out, view, ctx.row_slot, ctx.row_pos, n_rows, q_heads, scale, window, extra)
     elif ctx.decode:
         visible = min(v for v in (ctx.max_context, extra.chunk, window + extra.keep_first if window else 0) if v)

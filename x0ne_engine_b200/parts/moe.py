@@ -56,6 +56,7 @@ class RoutedExperts(FeedForward):
         if self.activation not in ("relu2", "swiglu"):
             raise ValueError(f"expert activation {self.activation!r} is not served; served: 'relu2', 'swiglu'")
         self.gated = self.activation == "swiglu"
+        self.pair_block = 0
         self.choice = g("choice", "scores") or "scores"
         if self.choice not in ("scores", "logits"):
             raise ValueError(f"router choice {self.choice!r} is not served; served: 'scores', 'logits'")
@@ -90,8 +91,16 @@ class RoutedExperts(FeedForward):
         rows = [tensors[n["router"]]] + ([tensors[n["shared_gate"]]] if self.shared_gate else [])
         self.router = Linear(torch.cat(rows, dim=0).contiguous())
         self.correction = tensors[n["correction"]]
-        if self.gated:      # [E, 2 ff, hidden]: an expert's gate rows, then its up rows
-            self.up = torch.stack([torch.cat([tensors[n["gate"].format(e=e)], tensors[n["up"].format(e=e)]], dim=0)
+        if self.gated:
+            # [E, 2 ff, hidden]: an expert's gate rows, then its up rows; where ff is a multiple of MOE_PAIR_BLOCK, in blocks of that
+            # many gate rows followed by the up rows of the same outputs, so that a tile of the tensor-core product holds both
+            b = self.pair_block = ops.MOE_PAIR_BLOCK if self.inter % ops.MOE_PAIR_BLOCK == 0 else 0
+
+            def packed(gate, up):
+                if not b:
+                    return torch.cat([gate, up], dim=0)
+                return torch.cat([gate.reshape(-1, b, self.hidden), up.reshape(-1, b, self.hidden)], dim=1).reshape(2 * self.inter, self.hidden)
+            self.up = torch.stack([packed(tensors[n["gate"].format(e=e)], tensors[n["up"].format(e=e)])
                                    for e in range(self.experts)]).contiguous()
         else:
             self.up = torch.stack([tensors[n["up"].format(e=e)] for e in range(self.experts)]).contiguous()   # [E, ff, hidden]
@@ -127,19 +136,19 @@ class RoutedExperts(FeedForward):
                       on_logits=self.choice == "logits")
         pairs = n_rows * top
         up_kind = 2 if self.gated else 0
-        if not self.gated and ops.moe_tc_takes(dt, pairs, self.hidden, self.inter):
+        if (not self.gated or self.pair_block) and ops.moe_tc_takes(dt, pairs, self.hidden, self.inter):
             # many pairs: tiles of 128 listed pairs on the tensor cores; the rows are gathered into the listed order first,
             # the activations stay in that order, the down product writes by pair
             n_tiles = ops.moe_max_tiles(pairs, self.experts, ops.MOE_TC_TILE_ROWS)
             xs = ws.buffer("moe.gathered", (rows * top, self.hidden), dt)
             ops.moe_group(chosen, pairs, self.experts, offsets, listed, tiles[:n_tiles], ops.MOE_TC_TILE_ROWS, n_real)
             ops.moe_gather_rows(x, listed, offsets, self.experts, top, xs, pairs)
-            ops.moe_product_tc(0, xs, self.up, listed, tiles, n_real, n_tiles, act)
+            ops.moe_product_tc(up_kind, xs, self.up, listed, tiles, n_real, n_tiles, act)
             ops.moe_product_tc(1, act, self.down, listed, tiles, n_real, n_tiles, y)
         else:
             n_tiles = ops.moe_max_tiles(pairs, self.experts)
             ops.moe_group(chosen, pairs, self.experts, offsets, listed, tiles[:n_tiles])
-            ops.moe_product(up_kind, x, self.up, listed, tiles, n_tiles, top, act)
+            ops.moe_product(up_kind, x, self.up, listed, tiles, n_tiles, top, act, self.pair_block)
             ops.moe_product(1, act, self.down, listed, tiles, n_tiles, top, y)
         shared = None
         if self.shared_size:
