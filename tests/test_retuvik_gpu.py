@@ -451,6 +451,34 @@ def test_scan_over_unequal_sequences_and_again_from_the_state(dtype, heads, n):
     assert float((state[1] - 7.0).abs().max()) == 0.0 and float(state[4].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,n", [(3, 10), (2, 32), (2, 64), (1, 100), (1, 128), (1, 200)])
+def test_one_token_steps_give_the_bits_of_the_scan_over_all_rows(dtype, heads, n):
+    """Three sequences of 21 rows in one launch, against the same rows fed one per sequence and launch through the
+    kernel for decode steps (slots in another order, a padding sequence in the middle): outputs and states bit for bit."""
+    from x0ne_engine_b200.csrc import ops
+    g = torch.Generator().manual_seed(11 + n)
+    width, hn, mats, T, B = 16, heads * n, heads * n * n, 21, 3
+    r, k, v, z, w0, u = scan_inputs(g, B * T, heads, n, dtype)
+    h = torch.randn(B * T, width, generator=g).to(dtype).to(DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)      # noqa: E731
+    state = (0.1 * torch.randn((4, mats + width), generator=g)).to(DEV)
+    state2 = state[[2, 0, 1, 3]].clone()                  # the same starts, held in slots 2 -> 0, 0 -> 1, 1 -> 2
+    o = torch.zeros((B * T, hn), dtype=torch.float32, device=DEV)
+    ops.wkv_scan(r, k, v, z, w0, u, h, o, state, i32([0, T, 2 * T, 3 * T]), i32([2, 0, 1]), B, heads, n)
+    o2 = torch.zeros_like(o)
+    for t in range(T):
+        rows = [t, T + t, 2 * T + t]
+        pick = lambda x: x[rows].contiguous()               # noqa: E731
+        ot = torch.zeros((B, hn), dtype=torch.float32, device=DEV)
+        ops.wkv_scan(pick(r), pick(k), pick(v), pick(z), w0, u, pick(h), ot, state2, i32([0, 1, 1, 2, 3]), i32([0, -1, 1, 2]), 4,
+                     heads, n, one_token=True)
+        o2[rows] = ot
+    assert torch.equal(o2, o)
+    assert torch.equal(state2[0], state[2]) and torch.equal(state2[1], state[0]) and torch.equal(state2[2], state[1])
+    assert torch.equal(state2[3], state[3])
+
+
 def test_scan_keeps_a_token_hundreds_of_rows_back():
     """One key channel of head 1 hardly decays and only the first token writes to it; a query 600 rows later reads
     that channel alone.  Its output is the first token's value (times the decays), so a state that is lost, reset

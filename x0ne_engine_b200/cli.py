@@ -556,7 +556,7 @@ def cmd_kernel_bench(a) -> int:
         w0, u = torch.randn(hn, device=dev) - 2.0, torch.randn(hn, device=dev)
         first = (torch.arange(B + 1, dtype=torch.int32, device=dev) * per).contiguous()
         slots = torch.arange(B, dtype=torch.int32, device=dev)
-        timed(lambda: ops.wkv_scan(r, k, v, z, w0, u, h, o, state, first, slots, B, heads, n),
+        timed(lambda: ops.wkv_scan(r, k, v, z, w0, u, h, o, state, first, slots, B, heads, n, one_token=per == 1),
               rows * hn * (3 * 2 + 4 + 4) + 2 * B * mats * 4, 4.0 * rows * hn * n)
         return 0
     if a.kernel == "head_norm_kv":

@@ -91,7 +91,7 @@ _SIGNATURES = {
     "x0ne_head_norm_kv_write": [_P, _I, _I, _I, _I, _P, _P, _F, _F, _I, _I, _P, _I, None, _P, _P, _I, _P],
     "x0ne_bias_act": [_P, _P, _P, _I, _I, _I, _I, _F, _F, _P],
     "x0ne_token_shift_mix": [_P, _I, _P, _I, _P, _L, _P, _L, _L, _P, _P, _I, _I, _P],
-    "x0ne_wkv_scan": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _P],
+    "x0ne_wkv_scan": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P],
     "x0ne_head_norm_gate": [_P, _P, _P, _P, _I, _I, _I, _I, _F, _P],
     "x0ne_tanh_rows": [_P, _P, _I, _L, _P],
     "x0ne_moe_group": [_P, _I, _I, _P, _P, _P, _I, _I, _P, _P],
@@ -1160,10 +1160,11 @@ def token_shift_mix(h: torch.Tensor, mu: torch.Tensor, mixes: torch.Tensor, stat
 
 def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, w0: torch.Tensor, u: torch.Tensor, h: torch.Tensor,
              o: torch.Tensor, state: torch.Tensor, seq_first_row: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int, heads: int,
-             n: int) -> None:
+             n: int, one_token: bool = False) -> None:
     """Per sequence and head, token by token over the sequence's rows, from and into its state [heads, n, n]:
     w = exp(-exp(z + w0)); o[j] = sum_i r[i] (S[i][j] + u[i] k[i] v[j]); S[i][j] = w[i] S[i][j] + k[i] v[j].  The last
-    row's h is left behind the matrices in the state row.  r, k, v, h in the activation type; z, o, state float32."""
+    row's h is left behind the matrices in the state row.  r, k, v, h in the activation type; z, o, state float32.
+    `one_token`: every sequence brings one row (a decode step); the kernel made for that runs, with the same bits."""
     lib = _lib("core")
     for t, what in ((r, "r"), (k, "k"), (v, "v"), (h, "mixer input")):
         _need(t, r.dtype, what)
@@ -1175,7 +1176,7 @@ def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
         raise KernelError("wkv_scan: shapes do not match")
     _check(lib, lib.x0ne_wkv_scan(_ptr(r), _ptr(k), _ptr(v), dtype_tag(r.dtype), _ptr(z), _ptr(w0), _ptr(u), _ptr(h), _ptr(o),
                                   _ptr(state), state.stride(0), _ptr(seq_first_row), _ptr(seq_slot), n_seqs, heads, n, width,
-                                  _stream()), "wkv_scan")
+                                  1 if one_token else 0, _stream()), "wkv_scan")
 
 
 def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, n_rows: int, heads: int, n: int,

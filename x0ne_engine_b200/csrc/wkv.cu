@@ -42,112 +42,258 @@ __global__ void token_shift_mix_kernel(const T* __restrict__ h, const float* __r
 }
 
 // ----------------------------------------------------------------------------------------
-// scan: one block per (sequence, head); WKV_P threads share column j of S, each with NB / WKV_P of its N values in
-// registers (key channels 4 (e WKV_P + p) + 0..3 for e = 0, 1, ...), so a token costs each thread NB / WKV_P steps of
-// the recurrence, four partial sums that do not wait on each other, and two shuffles.  The rows of the next 16 tokens
-// are fetched into registers while the current 16 are worked on out of shared memory.
+// scan.  The order of every sum is fixed and the same in both kernels below: out[j] is the sum over groups g of four
+// key channels of  p_g = fma chain over the group's channels ascending (from 0),  and the p_g are added as a balanced
+// tree (neighbours first).  So a token's result is the same bits whichever kernel ran it.
+//
+// wkv_scan_kernel (rows of many tokens): one block per (sequence, head, WKV_CB value columns of S); columns of S do
+// not depend on one another, so a head is spread over blocks.  Two kinds of threads:
+//   * 2 NB working threads: thread (g, jp) keeps the 4 x 2 tile of S at key channels 4 g .. 4 g + 3 and value columns
+//     2 jp, 2 jp + 1 of the block in registers.  A token costs it four reads of shared memory (r, k, w of its four
+//     channels, v of its two columns), 8 steps of the recurrence, one exchange with its neighbour in g (the first
+//     level of the tree: one of the two goes on with the first column, the other with the second) and one store of
+//     that sum to shared memory.  Only S is carried from token to token.
+//   * WKV_PRODUCERS staging threads: they fetch r, k, v and the decay exponents two stages ahead into registers, work
+//     out w = exp(-exp(z + w0)) and put all of it into the other half of a double buffer while the current half is
+//     used; then they add the partial sums of the stage before (the tree's other levels) and write out.
+// wkv_step_kernel (one token per sequence): one block per (sequence, head); thread (j, y) reads, uses and writes back
+// the values of column j in its groups straight from and to the state, coalesced over j.
 // ----------------------------------------------------------------------------------------
-#define WKV_TB 16      // tokens staged in shared memory at a time
-#define WKV_P 4        // threads per column of the state
+#define WKV_CB 16             // value columns of a block of the scan over many tokens
+#define WKV_GI 4              // key channels of a group
+#define WKV_PRODUCERS 128     // staging threads of a block
+
+template <int G>
+__device__ __forceinline__ float wkv_tree_sum(float (&q)[G]) {
+#pragma unroll
+    for (int w = 1; w < G; w <<= 1)
+#pragma unroll
+        for (int x = 0; x < G; x += 2 * w) q[x] += q[x + w];
+    return q[0];
+}
 
 template <typename T, int NB>
-__global__ void __launch_bounds__(NB * WKV_P) wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
-                                                             const float* __restrict__ z, const float* __restrict__ w0,
-                                                             const float* __restrict__ u, const T* __restrict__ h,
-                                                             float* __restrict__ o, float* __restrict__ state, int64_t state_stride,
-                                                             const int32_t* __restrict__ seq_first_row, const int32_t* __restrict__ seq_slot,
-                                                             int heads, int N, int width) {
-    constexpr int NT = NB * WKV_P;              // threads
-    constexpr int PER = NB / WKV_P;             // state values per thread
-    constexpr int FETCH = WKV_TB * NB / NT;     // values of each staged array a thread fetches per 16 tokens
-    static_assert(PER % 4 == 0 && WKV_TB * NB % NT == 0, "the column split must leave groups of four key channels");
-    __shared__ __align__(16) float rs[WKV_TB][NB], ks[WKV_TB][NB], ws[WKV_TB][NB], vs[WKV_TB][NB];
-    __shared__ __align__(16) float us[NB], w0s[NB];
+__global__ void __launch_bounds__(2 * NB + WKV_PRODUCERS) wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
+                                                                         const float* __restrict__ z, const float* __restrict__ w0,
+                                                                         const float* __restrict__ u, const T* __restrict__ h,
+                                                                         float* __restrict__ o, float* __restrict__ state, int64_t state_stride,
+                                                                         const int32_t* __restrict__ seq_first_row, const int32_t* __restrict__ seq_slot,
+                                                                         int heads, int N, int width) {
+    constexpr int G = NB / WKV_GI;                  // groups of key channels = working threads that share a column
+    constexpr int H = G / 2;                        // partial sums of a column that reach shared memory
+    constexpr int NC = G * (WKV_CB / 2);            // working threads: 2 NB
+    constexpr int TB = NB <= 64 ? 16 : 8;           // tokens staged at a time
+    constexpr int PER = TB * NB / WKV_PRODUCERS;    // values of r, k, z a staging thread fetches per stage
+    constexpr int PV = TB * WKV_CB / WKV_PRODUCERS; // values of v, and results it adds up
+    constexpr int TSTEP = WKV_PRODUCERS / NB;
+    static_assert(H >= 4 && (G & (G - 1)) == 0 && G <= 32 && WKV_PRODUCERS % NB == 0 && PER >= 1 && PV >= 1 && NC == 2 * NB, "tile shape");
+    __shared__ __align__(16) float rs[2][TB][NB], ks[2][TB][NB], ws[2][TB][NB], vs[2][TB][WKV_CB];
+    __shared__ __align__(16) float part[2][TB][WKV_CB][H];
     pdl_launch_dependents();
-    const int seq = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
-    const int j = tid / WKV_P, p = tid % WKV_P;
+    const int seq = blockIdx.x, head = blockIdx.y, j0 = blockIdx.z * WKV_CB, tid = threadIdx.x;
     const int64_t ld = (int64_t)heads * N;
-    for (int i = tid; i < NB; i += NT) {
-        us[i] = i < N ? u[head * N + i] : 0.f;
-        w0s[i] = i < N ? w0[head * N + i] : 0.f;
+    const bool producer = tid >= NC;
+    const int pt = tid - NC, pi = pt % NB, ptb = pt / NB;           // staging: its key channel and first token
+    const int g = tid % G, jc = 2 * ((tid / G) % (WKV_CB / 2)), i0 = WKV_GI * g;      // working: its tile
+    float w0r = 0.f, ur[WKV_GI];
+#pragma unroll
+    for (int a = 0; a < WKV_GI; ++a) ur[a] = 0.f;
+    if (producer) {
+        if (pi < N) w0r = w0[head * N + pi];
+    } else {
+#pragma unroll
+        for (int a = 0; a < WKV_GI; ++a)
+            if (i0 + a < N) ur[a] = u[head * N + i0 + a];
+    }
+    pdl_wait();
+    const int slot = seq_slot[seq];
+    const int row0 = seq_first_row[seq], row1 = seq_first_row[seq + 1];
+    if (slot < 0 || row1 <= row0 || j0 >= N) return;
+    float* S = state + (int64_t)slot * state_stride + (int64_t)head * N * N;
+    const int n_stages = (row1 - row0 + TB - 1) / TB;
+
+    float fr[PER], fk[PER], fz[PER], fv[PV];            // a staging thread's share of one stage, on its way
+    auto fetch = [&](int at_stage) {
+        const int t0 = row0 + at_stage * TB;
+#pragma unroll
+        for (int x = 0; x < PER; ++x) {
+            // every fetch is made, from an address inside the sequence's rows, so that none waits for another;
+            // rows past the sequence's last are not used, channels past the head's last are zeroed in `put`
+            const int64_t at = (int64_t)min(t0 + ptb + x * TSTEP, row1 - 1) * ld + (int64_t)head * N + min(pi, N - 1);
+            fr[x] = to_f32(r[at]);
+            fk[x] = to_f32(k[at]);
+            fz[x] = z[at];
+        }
+#pragma unroll
+        for (int x = 0; x < PV; ++x) {
+            const int e = pt + x * WKV_PRODUCERS, t = e / WKV_CB, c = e % WKV_CB;
+            fv[x] = to_f32(v[(int64_t)min(t0 + t, row1 - 1) * ld + (int64_t)head * N + min(j0 + c, N - 1)]);
+        }
+    };
+    auto put = [&](int buf) {
+#pragma unroll
+        for (int x = 0; x < PER; ++x) {
+            const int t = ptb + x * TSTEP;
+            rs[buf][t][pi] = pi < N ? fr[x] : 0.f;
+            ks[buf][t][pi] = pi < N ? fk[x] : 0.f;
+            ws[buf][t][pi] = pi < N ? expf(-expf(fz[x] + w0r)) : 0.f;
+        }
+#pragma unroll
+        for (int x = 0; x < PV; ++x) {
+            const int e = pt + x * WKV_PRODUCERS, c = e % WKV_CB;
+            vs[buf][e / WKV_CB][c] = j0 + c < N ? fv[x] : 0.f;
+        }
+    };
+    auto write_out = [&](int at_stage, int buf) {       // the results of a stage the working threads are done with
+        const int t0 = row0 + at_stage * TB;
+#pragma unroll
+        for (int x = 0; x < PV; ++x) {
+            const int e = pt + x * WKV_PRODUCERS, t = e / WKV_CB, c = e % WKV_CB;
+            if (t0 + t >= row1 || j0 + c >= N) continue;
+            float q[H];
+#pragma unroll
+            for (int y = 0; y < H; y += 4) {
+                const float4 q4 = *reinterpret_cast<const float4*>(&part[buf][t][c][y]);
+                q[y] = q4.x; q[y + 1] = q4.y; q[y + 2] = q4.z; q[y + 3] = q4.w;
+            }
+            o[(int64_t)(t0 + t) * ld + (int64_t)head * N + j0 + c] = wkv_tree_sum<H>(q);
+        }
+    };
+
+    float s[WKV_GI][2];
+    if (producer) {
+        fetch(0);
+        put(0);
+        if (n_stages > 1) fetch(1);
+    } else {
+#pragma unroll
+        for (int a = 0; a < WKV_GI; ++a)
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+                s[a][b] = (i0 + a < N && j0 + jc + b < N) ? S[(int64_t)(i0 + a) * N + j0 + jc + b] : 0.f;
+    }
+    __syncthreads();
+    for (int it = 0; it < n_stages; ++it) {
+        const int buf = it & 1;
+        if (producer) {
+            if (it + 1 < n_stages) put(buf ^ 1);            // fetched a whole stage ago
+            if (it + 2 < n_stages) fetch(it + 2);
+            if (it > 0) write_out(it - 1, buf ^ 1);
+        } else {
+            const int nt = min(TB, row1 - (row0 + it * TB));
+            const bool odd = (g & 1) != 0;
+            float* mine = &part[buf][0][jc + (odd ? 1 : 0)][g >> 1];
+#pragma unroll 4
+            for (int t = 0; t < nt; ++t) {
+                const float4 r4 = *reinterpret_cast<const float4*>(&rs[buf][t][i0]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&ks[buf][t][i0]);
+                const float4 w4 = *reinterpret_cast<const float4*>(&ws[buf][t][i0]);
+                const float2 v2 = *reinterpret_cast<const float2*>(&vs[buf][t][jc]);
+                const float rr[4] = {r4.x, r4.y, r4.z, r4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w};
+                const float ww[4] = {w4.x, w4.y, w4.z, w4.w}, vv[2] = {v2.x, v2.y};
+                float acc[2] = {0.f, 0.f};
+#pragma unroll
+                for (int a = 0; a < WKV_GI; ++a)
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        const float kv = kk[a] * vv[b];
+                        acc[b] = fmaf(rr[a], fmaf(ur[a], kv, s[a][b]), acc[b]);
+                        s[a][b] = fmaf(ww[a], s[a][b], kv);
+                    }
+                // groups g and g ^ 1: the even one goes on with the first column's sum, the odd one with the second's
+                const float sum = (odd ? acc[1] : acc[0]) + __shfl_xor_sync(0xffffffffu, odd ? acc[0] : acc[1], 1);
+                mine[t * (WKV_CB * H)] = sum;
+            }
+        }
+        __syncthreads();
+    }
+    if (producer) {
+        write_out(n_stages - 1, (n_stages - 1) & 1);
+    } else {
+#pragma unroll
+        for (int a = 0; a < WKV_GI; ++a)
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+                if (i0 + a < N && j0 + jc + b < N) S[(int64_t)(i0 + a) * N + j0 + jc + b] = s[a][b];
+    }
+    if (head == 0 && blockIdx.z == 0) {        // the last row's h, for the token shift of the sequence's next token
+        float* last = state + (int64_t)slot * state_stride + (int64_t)heads * N * N;
+        const T* hr = h + (int64_t)(row1 - 1) * width;
+        for (int c = tid; c < width; c += NC + WKV_PRODUCERS) last[c] = to_f32(hr[c]);
+    }
+}
+
+// One token per sequence (more are worked through one after the other): block (NB, GY); thread (j, y) takes the groups
+// y, y + GY, ... of column j.
+template <typename T, int NB, int GY>
+__global__ void __launch_bounds__(NB * GY) wkv_step_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
+                                                          const float* __restrict__ z, const float* __restrict__ w0,
+                                                          const float* __restrict__ u, const T* __restrict__ h,
+                                                          float* __restrict__ o, float* __restrict__ state, int64_t state_stride,
+                                                          const int32_t* __restrict__ seq_first_row, const int32_t* __restrict__ seq_slot,
+                                                          int heads, int N, int width) {
+    constexpr int G = NB / WKV_GI;
+    __shared__ __align__(16) float rs[NB], ks[NB], ws[NB], us[NB], w0s[NB];
+    __shared__ float part[G][NB];
+    pdl_launch_dependents();
+    const int seq = blockIdx.x, head = blockIdx.y, j = threadIdx.x, y0 = threadIdx.y, tid = threadIdx.y * NB + threadIdx.x;
+    const int64_t ld = (int64_t)heads * N;
+    if (tid < NB) {
+        us[tid] = tid < N ? u[head * N + tid] : 0.f;
+        w0s[tid] = tid < N ? w0[head * N + tid] : 0.f;
     }
     pdl_wait();
     const int slot = seq_slot[seq];
     const int row0 = seq_first_row[seq], row1 = seq_first_row[seq + 1];
     if (slot < 0 || row1 <= row0) return;
     float* S = state + (int64_t)slot * state_stride + (int64_t)head * N * N;
-    float s[PER];
-#pragma unroll
-    for (int e = 0; e < PER / 4; ++e)
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int i = 4 * (e * WKV_P + p) + q;
-            s[4 * e + q] = (i < N && j < N) ? S[(int64_t)i * N + j] : 0.f;
-        }
-    float fr[FETCH], fk[FETCH], fv[FETCH], fz[FETCH];
-    auto fetch = [&](int t0) {
-#pragma unroll
-        for (int x = 0; x < FETCH; ++x) {
-            const int e = tid + x * NT, t = e / NB, i = e % NB;
-            const bool in = i < N && t0 + t < row1;
-            const int64_t at = (int64_t)(t0 + t) * ld + (int64_t)head * N + i;
-            fr[x] = in ? to_f32(r[at]) : 0.f;
-            fk[x] = in ? to_f32(k[at]) : 0.f;
-            fv[x] = in ? to_f32(v[at]) : 0.f;
-            fz[x] = in ? z[at] : 0.f;
-        }
-    };
-    fetch(row0);
-    __syncthreads();                            // us, w0s
-    for (int t0 = row0; t0 < row1; t0 += WKV_TB) {
-        const int nt = min(WKV_TB, row1 - t0);
-#pragma unroll
-        for (int x = 0; x < FETCH; ++x) {
-            const int e = tid + x * NT, t = e / NB, i = e % NB;
-            rs[t][i] = fr[x];
-            ks[t][i] = fk[x];
-            vs[t][i] = fv[x];
-            ws[t][i] = i < N ? expf(-expf(fz[x] + w0s[i])) : 0.f;
-        }
+    for (int t = row0; t < row1; ++t) {
         __syncthreads();
-        if (t0 + WKV_TB < row1) fetch(t0 + WKV_TB);
-        for (int t = 0; t < nt; ++t) {
-            const float vj = vs[t][j];
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        if (tid < NB) {
+            const int64_t at = (int64_t)t * ld + (int64_t)head * N + tid;
+            const bool in = tid < N;
+            rs[tid] = in ? to_f32(r[at]) : 0.f;
+            ks[tid] = in ? to_f32(k[at]) : 0.f;
+            ws[tid] = in ? expf(-expf(z[at] + w0s[tid])) : 0.f;
+        }
+        const float vj = j < N ? to_f32(v[(int64_t)t * ld + (int64_t)head * N + j]) : 0.f;
+        float sv[(G + GY - 1) / GY][WKV_GI];
 #pragma unroll
-            for (int e = 0; e < PER / 4; ++e) {
-                const int i0 = 4 * (e * WKV_P + p);
-                const float4 r4 = *reinterpret_cast<const float4*>(&rs[t][i0]);
-                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][i0]);
-                const float4 w4 = *reinterpret_cast<const float4*>(&ws[t][i0]);
-                const float4 u4 = *reinterpret_cast<const float4*>(&us[i0]);
-                const float rr[4] = {r4.x, r4.y, r4.z, r4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w};
-                const float ww[4] = {w4.x, w4.y, w4.z, w4.w}, uu[4] = {u4.x, u4.y, u4.z, u4.w};
+        for (int x = 0; x < (G + GY - 1) / GY; ++x) {
+            const int g = y0 + x * GY;
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float kv = kk[q] * vj;
-                    acc[q] = fmaf(rr[q], fmaf(uu[q], kv, s[4 * e + q]), acc[q]);
-                    s[4 * e + q] = fmaf(ww[q], s[4 * e + q], kv);
-                }
+            for (int a = 0; a < WKV_GI; ++a) {
+                const int i = WKV_GI * g + a;
+                sv[x][a] = (g < G && i < N && j < N) ? S[(int64_t)i * N + j] : 0.f;
             }
-            float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-#pragma unroll
-            for (int off = 1; off < WKV_P; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-            if (p == 0 && j < N) o[(int64_t)(t0 + t) * ld + (int64_t)head * N + j] = sum;
         }
         __syncthreads();
-    }
 #pragma unroll
-    for (int e = 0; e < PER / 4; ++e)
+        for (int x = 0; x < (G + GY - 1) / GY; ++x) {
+            const int g = y0 + x * GY;
+            if (g >= G) continue;
+            float acc = 0.f;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int i = 4 * (e * WKV_P + p) + q;
-            if (i < N && j < N) S[(int64_t)i * N + j] = s[4 * e + q];
+            for (int a = 0; a < WKV_GI; ++a) {
+                const int i = WKV_GI * g + a;
+                const float kv = ks[i] * vj;
+                acc = fmaf(rs[i], fmaf(us[i], kv, sv[x][a]), acc);
+                if (i < N && j < N) S[(int64_t)i * N + j] = fmaf(ws[i], sv[x][a], kv);
+            }
+            part[g][j] = acc;
         }
-    if (head == 0) {        // the last row's h, for the token shift of the sequence's next token
+        __syncthreads();
+        if (y0 == 0 && j < N) {
+            float q[G];
+#pragma unroll
+            for (int x = 0; x < G; ++x) q[x] = part[x][j];
+            o[(int64_t)t * ld + (int64_t)head * N + j] = wkv_tree_sum<G>(q);
+        }
+    }
+    if (head == 0) {
         float* last = state + (int64_t)slot * state_stride + (int64_t)heads * N * N;
         const T* hr = h + (int64_t)(row1 - 1) * width;
-        for (int c = tid; c < width; c += NT) last[c] = to_f32(hr[c]);
+        for (int c = tid; c < width; c += NB * GY) last[c] = to_f32(hr[c]);
     }
 }
 
@@ -240,34 +386,37 @@ X0NE_API int x0ne_token_shift_mix(const void* h, int dt, const float* mu, int n_
 template <typename T>
 static int wkv_scan_launch(const T* r, const T* k, const T* v, const float* z, const float* w0, const float* u, const T* h, float* o,
                            float* state, int64_t state_stride, const int32_t* seq_first_row, const int32_t* seq_slot, int n_seqs,
-                           int heads, int N, int width, cudaStream_t stream) {
+                           int heads, int N, int width, int one_token, cudaStream_t stream) {
     const dim3 grid(n_seqs, heads);
-#define WKV_SCAN(NB) x0ne_launch(wkv_scan_kernel<T, NB>, grid, dim3(NB * WKV_P), 0, stream, r, k, v, z, w0, u, h, o, state, state_stride, seq_first_row, seq_slot, heads, N, width)
-    if (N <= 32) WKV_SCAN(32);
-    else if (N <= 64) WKV_SCAN(64);
-    else if (N <= 96) WKV_SCAN(96);
-    else if (N <= 128) WKV_SCAN(128);
+#define WKV_ARGS r, k, v, z, w0, u, h, o, state, state_stride, seq_first_row, seq_slot, heads, N, width
+#define WKV_SCAN(NB) x0ne_launch(wkv_scan_kernel<T, NB>, dim3(n_seqs, heads, NB / WKV_CB), dim3(2 * NB + WKV_PRODUCERS), 0, stream, WKV_ARGS)
+#define WKV_STEP(NB, GY) x0ne_launch(wkv_step_kernel<T, NB, GY>, grid, dim3(NB, GY), 0, stream, WKV_ARGS)
+    if (N <= 32) { if (one_token) WKV_STEP(32, 4); else WKV_SCAN(32); }
+    else if (N <= 64) { if (one_token) WKV_STEP(64, 8); else WKV_SCAN(64); }
+    else if (N <= 128) { if (one_token) WKV_STEP(128, 4); else WKV_SCAN(128); }
     else {
         const int threads = N >= 256 ? 256 : (N + 31) / 32 * 32;
-        x0ne_launch(wkv_scan_any_kernel<T>, grid, dim3(threads), (size_t)3 * N * sizeof(float), stream, r, k, v, z, w0, u, h, o, state, state_stride,
-                    seq_first_row, seq_slot, heads, N, width);
+        x0ne_launch(wkv_scan_any_kernel<T>, grid, dim3(threads), (size_t)3 * N * sizeof(float), stream, WKV_ARGS);
     }
 #undef WKV_SCAN
+#undef WKV_STEP
+#undef WKV_ARGS
     X0NE_LAUNCH_CHECK();
 }
 
 // r, k, v: [rows][heads * N] in the activation type; z: float32 [rows][heads * N] (the decay's exponent before w0);
 // h: [rows][width], the mixer's input; o: float32 [rows][heads * N]; state: float32 [slots][state_stride].
+// one_token != 0 says that every sequence brings one row (the kernel made for that runs; it is right for any number).
 X0NE_API int x0ne_wkv_scan(const void* r, const void* k, const void* v, int dt, const float* z, const float* w0, const float* u,
                            const void* h, float* o, float* state, int64_t state_stride, const int32_t* seq_first_row,
-                           const int32_t* seq_slot, int n_seqs, int heads, int N, int width, cudaStream_t stream) {
+                           const int32_t* seq_slot, int n_seqs, int heads, int N, int width, int one_token, cudaStream_t stream) {
     X0NE_REQUIRE(n_seqs >= 0 && heads > 0 && heads <= 65535 && N > 0 && N <= 4096 && width > 0 && state_stride >= (int64_t)heads * N * N + width,
                  "wkv_scan: %d sequences, %d heads of %d, width %d", n_seqs, heads, N, width);
     if (n_seqs == 0) return 0;
     if (dt == X0NE_F32)
-        return wkv_scan_launch<float>((const float*)r, (const float*)k, (const float*)v, z, w0, u, (const float*)h, o, state, state_stride, seq_first_row, seq_slot, n_seqs, heads, N, width, stream);
+        return wkv_scan_launch<float>((const float*)r, (const float*)k, (const float*)v, z, w0, u, (const float*)h, o, state, state_stride, seq_first_row, seq_slot, n_seqs, heads, N, width, one_token, stream);
     if (dt == X0NE_BF16)
-        return wkv_scan_launch<bf16>((const bf16*)r, (const bf16*)k, (const bf16*)v, z, w0, u, (const bf16*)h, o, state, state_stride, seq_first_row, seq_slot, n_seqs, heads, N, width, stream);
+        return wkv_scan_launch<bf16>((const bf16*)r, (const bf16*)k, (const bf16*)v, z, w0, u, (const bf16*)h, o, state, state_stride, seq_first_row, seq_slot, n_seqs, heads, N, width, one_token, stream);
     X0NE_REQUIRE(false, "wkv_scan: unknown dtype tag %d", dt);
 }
 

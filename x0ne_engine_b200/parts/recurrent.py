@@ -94,7 +94,7 @@ class MatrixStateRecurrence(Mixer):
         self.w2(low_t, z, n_rows)
         o = ws.buffer("wkv.o", (rows, self.hn), torch.float32)
         ops.wkv_scan(out["r"], out["k"], out["v"], z, self.w0, self.u, x, o, state, ctx.seq_first_row, ctx.seq_slot, ctx.n_seqs,
-                     self.heads, self.n)
+                     self.heads, self.n, one_token=ctx.decode)
         gated = ws.buffer("wkv.gated", (rows, self.hn), dt)
         ops.head_norm_gate(o, self.norm, out["g"], gated, n_rows, self.heads, self.n, self.eps)
         delta = ws.buffer("delta", (rows, self.hidden), dt)
