@@ -41,6 +41,59 @@ __global__ void token_shift_mix_kernel(const T* __restrict__ h, const float* __r
     }
 }
 
+// 8 consecutive values as 16-byte accesses
+__device__ __forceinline__ void wkv_load8(const bf16* p, float* v) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h2[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void wkv_load8(const float* p, float* v) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void wkv_store8(bf16* p, const float* v) {
+    uint4 q;
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h2[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = q;
+}
+__device__ __forceinline__ void wkv_store8(float* p, const float* v) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+// The token shift with 8 values per thread (width, strides and offsets multiples of 8, 16-byte aligned bases):
+// block (row, 8 x blockDim.x columns).
+template <typename T>
+__global__ void token_shift_mix_vec_kernel(const T* __restrict__ h, const float* __restrict__ mu, int n_mix, T* __restrict__ mixes,
+                                           int64_t mix_stride, const float* __restrict__ state, int64_t state_stride,
+                                           int64_t last_off, const int32_t* __restrict__ row_slot,
+                                           const int32_t* __restrict__ row_pos, int n_rows, int width) {
+    pdl_prologue();
+    const int row = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (c >= width) return;
+    const int slot = row_slot[row], pos = row_pos[row];
+    const bool above = row > 0 && slot >= 0 && row_slot[row - 1] == slot && row_pos[row - 1] == pos - 1;
+    const T* cur = h + (int64_t)row * width + c;
+    float x[8], b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    wkv_load8(cur, x);
+    if (above) wkv_load8(cur - width, b);
+    else if (slot >= 0) wkv_load8(state + (int64_t)slot * state_stride + last_off + c, b);
+    for (int s = 0; s < n_mix; ++s) {
+        float m[8], y[8];
+        wkv_load8(mu + (int64_t)s * width + c, m);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = fmaf(b[i] - x[i], m[i], x[i]);
+        wkv_store8(mixes + (int64_t)s * mix_stride + (int64_t)row * width + c, y);
+    }
+}
+
 // ----------------------------------------------------------------------------------------
 // scan.  The order of every sum is fixed and the same in both kernels below: out[j] is the sum over groups g of four
 // key channels of  p_g = fma chain over the group's channels ascending (from 0),  and the p_g are added as a balanced
@@ -364,6 +417,32 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
     }
 }
 
+// The same with 8 values per lane: LANES = N / 8 lanes (a power of two up to 32) work on one (row, head).
+template <typename T, int LANES>
+__global__ void head_norm_gate_vec_kernel(const float* __restrict__ o, const float* __restrict__ weight, const T* __restrict__ gate,
+                                          T* __restrict__ out, int64_t items, int heads, float eps) {
+    pdl_prologue();
+    constexpr int N = LANES * 8;
+    const int64_t item = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / LANES;
+    const int part = threadIdx.x % LANES;
+    const bool live = item < items;
+    const int64_t at = (live ? item : 0) * N + part * 8;
+    float x[8], g[8], w[8], y[8];
+    wkv_load8(o + at, x);
+    wkv_load8(gate + at, g);
+    wkv_load8(weight + (int)((live ? item : 0) % heads) * N + part * 8, w);
+    // the order of the scalar kernel's sum is not kept: the result is the same to rounding
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
+#pragma unroll
+    for (int off = LANES / 2; off >= 1; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float scale = 1.0f / sqrtf(ss / (float)N + eps);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = x[i] * scale * w[i] * (g[i] / (1.0f + expf(-g[i])));
+    if (live) wkv_store8(out + at, y);
+}
+
 // ----------------------------------------------------------------------------------------
 // host side
 // ----------------------------------------------------------------------------------------
@@ -373,6 +452,16 @@ X0NE_API int x0ne_token_shift_mix(const void* h, int dt, const float* mu, int n_
     X0NE_REQUIRE(n_rows >= 0 && width > 0 && n_mix > 0 && mix_stride >= (int64_t)n_rows * width && state_stride >= last_off + width,
                  "token_shift: rows %d width %d mixes %d", n_rows, width, n_mix);
     if (n_rows == 0) return 0;
+    if ((dt == X0NE_F32 || dt == X0NE_BF16) && width % 8 == 0 && mix_stride % 8 == 0 && state_stride % 4 == 0 && last_off % 4 == 0 &&
+        ((((uintptr_t)h | (uintptr_t)mu | (uintptr_t)mixes | (uintptr_t)state) & 15) == 0)) {
+        const int vthreads = width / 8 >= 128 ? 128 : (width / 8 + 31) / 32 * 32;
+        const dim3 vgrid(n_rows, (width / 8 + vthreads - 1) / vthreads);
+        if (dt == X0NE_F32)
+            x0ne_launch(token_shift_mix_vec_kernel<float>, vgrid, dim3(vthreads), 0, stream, (const float*)h, mu, n_mix, (float*)mixes, mix_stride, state, state_stride, last_off, row_slot, row_pos, n_rows, width);
+        else
+            x0ne_launch(token_shift_mix_vec_kernel<bf16>, vgrid, dim3(vthreads), 0, stream, (const bf16*)h, mu, n_mix, (bf16*)mixes, mix_stride, state, state_stride, last_off, row_slot, row_pos, n_rows, width);
+        X0NE_LAUNCH_CHECK();
+    }
     const int threads = width >= 256 ? 256 : (width + 31) / 32 * 32;
     if (dt == X0NE_F32)
         x0ne_launch(token_shift_mix_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (const float*)h, mu, n_mix, (float*)mixes, mix_stride, state, state_stride, last_off, row_slot, row_pos, n_rows, width);
@@ -426,6 +515,25 @@ X0NE_API int x0ne_head_norm_gate(const float* o, const float* weight, const void
     if (n_rows == 0) return 0;
     const int warps = 4;
     const int64_t items = (int64_t)n_rows * heads;
+    const int lanes = N / 8;
+    if ((dt == X0NE_F32 || dt == X0NE_BF16) && N % 8 == 0 && (lanes & (lanes - 1)) == 0 && lanes <= 32 &&
+        ((((uintptr_t)o | (uintptr_t)weight | (uintptr_t)gate | (uintptr_t)out) & 15) == 0)) {
+        const int per_block = 128 / lanes;
+        const dim3 vgrid((unsigned)((items + per_block - 1) / per_block));
+#define HNG(L)                                                                                                                        \
+        if (dt == X0NE_F32) x0ne_launch(head_norm_gate_vec_kernel<float, L>, vgrid, dim3(128), 0, stream, o, weight, (const float*)gate, (float*)out, items, heads, eps); \
+        else x0ne_launch(head_norm_gate_vec_kernel<bf16, L>, vgrid, dim3(128), 0, stream, o, weight, (const bf16*)gate, (bf16*)out, items, heads, eps)
+        switch (lanes) {
+            case 1: HNG(1); break;
+            case 2: HNG(2); break;
+            case 4: HNG(4); break;
+            case 8: HNG(8); break;
+            case 16: HNG(16); break;
+            default: HNG(32); break;
+        }
+#undef HNG
+        X0NE_LAUNCH_CHECK();
+    }
     const unsigned grid = (unsigned)((items + warps - 1) / warps);
     if (dt == X0NE_F32)
         x0ne_launch(head_norm_gate_kernel<float>, dim3(grid), dim3(warps * 32), 0, stream, o, weight, (const float*)gate, (float*)out, n_rows, heads, N, eps);
