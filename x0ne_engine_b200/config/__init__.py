@@ -9,11 +9,14 @@ from .tenetar import ARCHITECTURE as _TENETAR, MODEL_TYPE as _TENETAR_TYPE, Tene
 
 from .retuvik import ARCHITECTURE as _RETUVIK, MODEL_TYPE as _RETUVIK_TYPE, RetuvikConfig
 
+from .barorax import ARCHITECTURE as _BARORAX, MODEL_TYPE as _BARORAX_TYPE, BaroraxConfig
+
 register_architecture(_QWEN3, _QWEN3_TYPE, Qwen3Config)
 register_architecture(_TENETAR, _TENETAR_TYPE, TenetarConfig)
 register_architecture(_ROVURAX, _ROVURAX_TYPE, RovuraxConfig)
 register_architecture(_RETUVIK, _RETUVIK_TYPE, RetuvikConfig)
+register_architecture(_BARORAX, _BARORAX_TYPE, BaroraxConfig)
 
-__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "Qwen3Config", "RovuraxConfig", "TenetarConfig", "RetuvikConfig",
+__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "Qwen3Config", "RovuraxConfig", "TenetarConfig", "RetuvikConfig", "BaroraxConfig",
            "architectures", "config_from_dict", "config_from_folder", "detect",
            "register_architecture", "spec_from_folder", "unregister_architecture"]

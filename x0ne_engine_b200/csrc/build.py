@@ -32,7 +32,7 @@ NVCC_FLAGS += shlex.split(os.environ.get("X0NE_NVCC_FLAGS", ""))
 
 # module name -> sources.  `core` is all a 32-bit run needs; `fast` holds the bfloat16 kernels.
 MODULES: Dict[str, List[str]] = {
-    "core": ["elementwise.cu", "mixer_rows.cu", "attention_generic.cu", "gemm_f32.cu", "moe.cu", "wkv.cu", "sampling.cu", "step_plan.cu"],
+    "core": ["elementwise.cu", "mixer_rows.cu", "attention_generic.cu", "gemm_f32.cu", "moe.cu", "wkv.cu", "ssm.cu", "sampling.cu", "step_plan.cu"],
     "fast": ["attention_bf16.cu", "gemm_bf16.cu", "fast_common.cu"],
     "flex": ["attention_flex.cu", "fast_common.cu"],
     "noalloc": ["attention_decode_noalloc.cu"],

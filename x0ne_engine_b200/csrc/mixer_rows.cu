@@ -771,3 +771,162 @@ X0NE_API int x0ne_bias_act(const void* x, const float* bias, void* out, int dt, 
     else x0ne_launch(bias_act_kernel<bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)x, bias, (bf16*)out, width, total, act, a, b);
     X0NE_LAUNCH_CHECK();
 }
+
+// ----------------------------------------------------------------------------------------
+// Preparation of an attention that rotates interleaved pairs and may hold several score maps per head.  src holds, per
+// row, the queries at column 0 (q_heads x maps x dim), the keys at k_col (kv_heads x maps x dim) and the values at v_col
+// (kv_heads x value width).  Of every (head, map) the first `rot` values are pairs (2i, 2i + 1) that turn by
+// pos * freq[i]: (u, v) -> (u cos - v sin, v cos + u sin); `table` (float32 [positions][rot]: rot/2 cosines, then rot/2
+// sines) replaces the computation for the positions it covers.  With unit_eps >= 0 every (head, map), after its rotation,
+// is divided by sqrt(mean(x^2) + unit_eps) over its dim values.  A kv head's maps lie side by side in its key row of
+// maps x dim values.  Queries go to q_out as [rows][q_heads x maps][dim], or, with `q_padded`, as [rows][q_heads x maps]
+// [maps x dim] with map m's values at column m x dim and zeros beside them: such a query, met with the whole key row,
+// scores against its own map alone.  One warp per (row, head and map of q or k, or value head); rows without a page
+// write no keys or values.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_pairs_kv_write_kernel(const T* __restrict__ src, int ld, int k_col, int v_col, const float* __restrict__ freq,
+                                           const float* __restrict__ table, int table_positions, int rot, int maps, int dim,
+                                           float unit_eps, T* __restrict__ q_out, int q_heads, int q_padded, PagedCache cache,
+                                           const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos, int n_rows,
+                                           int write_kv) {
+    pdl_prologue();
+    const int lane = threadIdx.x & 31;
+    const int nq = q_heads * maps, nk = cache.kv_heads * maps;
+    const int units = nq + nk + cache.kv_heads;
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (int64_t)n_rows * units) return;
+    const int row = (int)(item / units), unit = (int)(item % units);
+    const int pos = row_pos[row], slot = row_slot[row];
+    const T* s = src + (int64_t)row * ld;
+    if (unit >= nq + nk) {                        // a value head: copied as it is
+        const int g = unit - nq - nk, vd = cache_v_dim(cache);
+        const int64_t off = write_kv ? cache_row_offset(cache, slot, pos, g, 1) : -1;
+        if (off < 0) return;
+        T* dst = (T*)cache.base + off;
+        for (int i = lane; i < vd; i += 32) dst[i] = s[v_col + (int64_t)g * vd + i];
+        return;
+    }
+    const bool is_q = unit < nq;
+    const int sub = is_q ? unit : unit - nq;      // head x maps + map
+    const T* x = s + (is_q ? 0 : k_col) + (int64_t)sub * dim;
+    T* dst;
+    if (is_q) {
+        const int w = q_padded ? maps * dim : dim;
+        dst = q_out + ((int64_t)row * nq + sub) * w;
+        if (q_padded) {
+            for (int i = lane; i < w; i += 32)
+                if (i / dim != sub % maps) dst[i] = from_f32<T>(0.f);
+            dst += (sub % maps) * dim;
+        }
+    } else {
+        const int64_t off = write_kv ? cache_row_offset(cache, slot, pos, sub / maps, 0) : -1;
+        if (off < 0) return;
+        dst = (T*)cache.base + off + (sub % maps) * dim;
+    }
+    const int half = rot / 2, pairs = (dim + 1) / 2;
+    const bool tabled = pos >= 0 && pos < table_positions && table != nullptr;
+    // two passes over the pairs this lane owns: the sum of squares of the rotated values, then the values themselves
+    float scale = 1.f;
+    for (int pass = unit_eps >= 0.f ? 0 : 1; pass < 2; ++pass) {
+        float ss = 0.f;
+        for (int p = lane; p < pairs; p += 32) {
+            float u = to_f32(x[2 * p]), v = 2 * p + 1 < dim ? to_f32(x[2 * p + 1]) : 0.f;
+            if (p < half) {
+                float c, sn;
+                if (tabled) {
+                    c = table[(int64_t)pos * rot + p];
+                    sn = table[(int64_t)pos * rot + half + p];
+                } else {
+                    sincosf((float)pos * freq[p], &sn, &c);
+                }
+                const float ru = u * c - v * sn, rv = v * c + u * sn;
+                u = ru;
+                v = rv;
+            }
+            if (pass == 0) {
+                ss = fmaf(u, u, ss);
+                ss = fmaf(v, v, ss);
+            } else {
+                dst[2 * p] = from_f32<T>(u * scale);
+                if (2 * p + 1 < dim) dst[2 * p + 1] = from_f32<T>(v * scale);
+            }
+        }
+        if (pass == 0) scale = 1.0f / sqrtf(warp_sum(ss) / (float)dim + unit_eps);
+    }
+}
+
+X0NE_API int x0ne_rope_pairs_kv_write(const void* src, int dt, int ld, int k_col, int v_col, const float* freq, const float* table,
+                                      int table_positions, int rot, int maps, int dim, float unit_eps, void* q_out, int q_heads,
+                                      int q_padded, PagedCache cache, const int32_t* row_slot, const int32_t* row_pos, int n_rows,
+                                      int write_kv, cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && q_heads > 0 && maps > 0 && dim > 0 && rot >= 0 && rot % 2 == 0 && rot <= dim && cache.kv_heads > 0,
+                 "rope_pairs: heads %d maps %d dim %d rot %d", q_heads, maps, dim, rot);
+    X0NE_REQUIRE(cache.head_dim == maps * dim && cache.v_dim >= 0, "rope_pairs: the cache's key rows hold %d values, not %d maps of %d", cache.head_dim, maps, dim);
+    X0NE_REQUIRE(rot == 0 || freq != nullptr, "rope_pairs: no frequencies");
+    const int vd = cache_v_dim(cache);
+    X0NE_REQUIRE(k_col >= q_heads * maps * dim && v_col >= k_col + cache.kv_heads * maps * dim && ld >= v_col + cache.kv_heads * vd,
+                 "rope_pairs: columns %d, %d do not fit rows of %d", k_col, v_col, ld);
+    if (n_rows == 0) return 0;
+    const int warps = 4;
+    const int64_t items = (int64_t)n_rows * (q_heads * maps + cache.kv_heads * maps + cache.kv_heads);
+    X0NE_REQUIRE((items + warps - 1) / warps <= 0x7fffffff, "rope_pairs: too many rows");
+    const dim3 grid((unsigned)((items + warps - 1) / warps));
+    if (dt == X0NE_F32)
+        x0ne_launch(rope_pairs_kv_write_kernel<float>, grid, dim3(warps * 32), 0, stream, (const float*)src, ld, k_col, v_col, freq, table,
+                    table_positions, rot, maps, dim, unit_eps, (float*)q_out, q_heads, q_padded, cache, row_slot, row_pos, n_rows, write_kv);
+    else if (dt == X0NE_BF16)
+        x0ne_launch(rope_pairs_kv_write_kernel<bf16>, grid, dim3(warps * 32), 0, stream, (const bf16*)src, ld, k_col, v_col, freq, table,
+                    table_positions, rot, maps, dim, unit_eps, (bf16*)q_out, q_heads, q_padded, cache, row_slot, row_pos, n_rows, write_kv);
+    else
+        X0NE_REQUIRE(false, "rope_pairs: unknown dtype tag %d", dt);
+    X0NE_LAUNCH_CHECK();
+}
+
+// ----------------------------------------------------------------------------------------
+// Differential heads.  att holds, per row, heads x 2 results of vd values (map 1, then map 2 of each head):
+//   o = a1 - lambda a2;  out[row][head] = o / sqrt(mean(o^2) + eps) * post * sigmoid(gate[row][head x vd + d])
+// (gate null: no gate).  One warp per (row, head); the difference, the norm and the gate are float32.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void diff_heads_kernel(const T* __restrict__ att, const T* __restrict__ gate, int64_t gate_ld, T* __restrict__ out, int n_rows,
+                                  int heads, int vd, float lambda, float eps, float post) {
+    pdl_prologue();
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (int64_t)n_rows * heads) return;
+    const int row = (int)(item / heads), head = (int)(item % heads);
+    const T* a1 = att + ((int64_t)row * heads + head) * 2 * vd;
+    const T* a2 = a1 + vd;
+    float ss = 0.f;
+    for (int i = lane; i < vd; i += 32) {
+        const float o = to_f32(a1[i]) - lambda * to_f32(a2[i]);
+        ss = fmaf(o, o, ss);
+    }
+    const float scale = post / sqrtf(warp_sum(ss) / (float)vd + eps);
+    T* dst = out + ((int64_t)row * heads + head) * vd;
+    const T* g = gate != nullptr ? gate + (int64_t)row * gate_ld + (int64_t)head * vd : nullptr;
+    for (int i = lane; i < vd; i += 32) {
+        float o = (to_f32(a1[i]) - lambda * to_f32(a2[i])) * scale;
+        if (g != nullptr) o *= 1.0f / (1.0f + expf(-to_f32(g[i])));
+        dst[i] = from_f32<T>(o);
+    }
+}
+
+X0NE_API int x0ne_diff_heads(const void* att, const void* gate, int64_t gate_ld, void* out, int dt, int n_rows, int heads, int vd,
+                             float lambda, float eps, float post, cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && heads > 0 && vd > 0 && (gate == nullptr || gate_ld >= (int64_t)heads * vd), "diff_heads: rows %d heads %d of %d", n_rows, heads, vd);
+    if (n_rows == 0) return 0;
+    const int warps = 4;
+    const int64_t items = (int64_t)n_rows * heads;
+    const dim3 grid((unsigned)((items + warps - 1) / warps));
+    if (dt == X0NE_F32)
+        x0ne_launch(diff_heads_kernel<float>, grid, dim3(warps * 32), 0, stream, (const float*)att, (const float*)gate, gate_ld, (float*)out,
+                    n_rows, heads, vd, lambda, eps, post);
+    else if (dt == X0NE_BF16)
+        x0ne_launch(diff_heads_kernel<bf16>, grid, dim3(warps * 32), 0, stream, (const bf16*)att, (const bf16*)gate, gate_ld, (bf16*)out,
+                    n_rows, heads, vd, lambda, eps, post);
+    else
+        X0NE_REQUIRE(false, "diff_heads: unknown dtype tag %d", dt);
+    X0NE_LAUNCH_CHECK();
+}

@@ -8,6 +8,9 @@
 //   weights  the chosen outputs' s, as they are
 // or, for a router that chooses on its logits (`on_logits`): s = z + correction (a bias of the router) without a
 // softmax, the `top` largest s are chosen, and the weights are the softmax over the chosen s alone.
+// A third kind of router (`mode` 2) scores with s = sigmoid(z) (+ correction for the choice, if there is one).  For every kind a
+// group may be worth the sum of its `group_top` largest values instead of its largest one, and the chosen weights may
+// be divided by their sum (+ 1e-20) and multiplied by a constant (`normalize`, `weight_scale`).
 // The last `n - experts` router outputs are identity experts: their output is the row itself, they
 // have no weights and form no group of pairs.
 //
@@ -30,7 +33,7 @@
 // ----------------------------------------------------------------------------------------
 __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ correction, int n, int groups,
                                  int keep, int top, int n_rows, int32_t* __restrict__ chosen, float* __restrict__ weights,
-                                 float* __restrict__ sgate, int sg_col, int on_logits) {
+                                 float* __restrict__ sgate, int sg_col, int mode, int group_top, int normalize, float weight_scale) {
     extern __shared__ float rt_smem[];
     pdl_prologue();
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -40,10 +43,16 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, const flo
     float* c = s + n;                                       // choice values
     float* gv = c + n;                                      // group values
     const float* zr = z + (int64_t)row * ldz;
+    const bool on_logits = mode == 1;
     if (on_logits) {
         for (int i = lane; i < n; i += 32) {
             s[i] = zr[i] + correction[i];
             c[i] = s[i];
+        }
+    } else if (mode == 2) {
+        for (int i = lane; i < n; i += 32) {
+            s[i] = 1.0f / (1.0f + expf(-zr[i]));
+            c[i] = correction != nullptr ? s[i] + correction[i] : s[i];
         }
     } else {
         float m = -INFINITY;
@@ -66,7 +75,28 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, const flo
     if (groups > 1 && keep < groups) {
         for (int g = lane; g < groups; g += 32) {
             float b = -INFINITY;
-            for (int i = 0; i < per; ++i) b = fmaxf(b, c[g * per + i]);
+            if (group_top <= 1) {
+                for (int i = 0; i < per; ++i) b = fmaxf(b, c[g * per + i]);
+            } else {
+                // the sum of the group's `group_top` largest values, taken one after the other (a value taken is passed over
+                // by its index, so equal values count as often as they occur)
+                float sum = 0.f, last = INFINITY;
+                int last_i = -1;
+                for (int r = 0; r < group_top && r < per; ++r) {
+                    float bv = -INFINITY;
+                    int bi = -1;
+                    for (int i = 0; i < per; ++i) {
+                        const float v = c[g * per + i];
+                        const bool open = v < last || (v == last && i > last_i);
+                        if (open && (v > bv || bi < 0)) { bv = v; bi = i; }
+                    }
+                    if (bi < 0) break;
+                    sum += bv;
+                    last = bv;
+                    last_i = bi;
+                }
+                b = sum;
+            }
             gv[g] = b;
         }
         __syncwarp();
@@ -120,6 +150,12 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, const flo
             sum += wr[r];
         }
         for (int r = 0; r < top; ++r) wr[r] = wr[r] / sum;
+    }
+    if (normalize && lane == 0) {       // the chosen scores over their sum, times the router's scale, in the order they were chosen
+        float* wr = weights + (int64_t)row * top;
+        float sum = 0.f;
+        for (int r = 0; r < top; ++r) sum += wr[r];
+        for (int r = 0; r < top; ++r) wr[r] = wr[r] / (sum + 1e-20f) * weight_scale;
     }
     if (sgate != nullptr && lane == 0) sgate[row] = 1.0f / (1.0f + expf(-zr[sg_col]));
 }
@@ -366,8 +402,10 @@ X0NE_API int x0ne_moe_max_tiles(int pairs, int experts, int tile_m) {
 }
 
 X0NE_API int x0ne_moe_route(const float* z, int ldz, const float* correction, int n, int groups, int keep, int top, int n_rows,
-                            int32_t* chosen, float* weights, float* sgate, int sg_col, int on_logits, cudaStream_t stream) {
+                            int32_t* chosen, float* weights, float* sgate, int sg_col, int mode, int group_top, int normalize,
+                            float weight_scale, cudaStream_t stream) {
     X0NE_REQUIRE(n_rows >= 0 && n > 0 && ldz >= n && top > 0 && top <= n, "moe_route: rows %d outputs %d ld %d top %d", n_rows, n, ldz, top);
+    X0NE_REQUIRE(mode >= 0 && mode <= 2 && group_top >= 1 && (correction != nullptr || mode == 2), "moe_route: mode %d, group worth of %d values", mode, group_top);
     X0NE_REQUIRE(groups >= 1 && n % groups == 0 && keep >= 1 && keep <= groups && top <= keep * (n / groups),
                  "moe_route: %d outputs in %d groups of which %d stay cannot give %d choices", n, groups, keep, top);
     X0NE_REQUIRE(sgate == nullptr || (sg_col >= n && sg_col < ldz), "moe_route: the shared gate's column %d lies outside the rows", sg_col);
@@ -376,7 +414,7 @@ X0NE_API int x0ne_moe_route(const float* z, int ldz, const float* correction, in
     const size_t smem = (size_t)warps * (2 * n + groups) * sizeof(float);
     X0NE_REQUIRE(smem <= 48 * 1024, "moe_route: %d router outputs are more than the kernel holds", n);
     x0ne_launch(moe_route_kernel, dim3((n_rows + warps - 1) / warps), dim3(warps * 32), smem, stream, z, ldz, correction, n, groups, keep,
-                top, n_rows, chosen, weights, sgate, sg_col, on_logits);
+                top, n_rows, chosen, weights, sgate, sg_col, mode, group_top, normalize, weight_scale);
     X0NE_LAUNCH_CHECK();
 }
 

@@ -65,6 +65,14 @@ def attn_extra(chunk: int = 0, v_from_k: int = 0, sink: Optional[torch.Tensor] =
                         1 if gate_wide else 0, _ptr(slope))
 
 
+class SsmArg(Structure):
+    """Mirror of `struct SsmArgs` in ssm.cu."""
+    _fields_ = [("u", c_void_p), ("xz", c_void_p), ("xz_ld", c_int64), ("z_col", c_int32), ("dt_raw", c_void_p), ("dt_bias", c_void_p),
+                ("A", c_void_p), ("bc", c_void_p), ("bc_ld", c_int64), ("b_col", c_int32), ("c_col", c_int32), ("D", c_void_p),
+                ("out", c_void_p), ("state", c_void_p), ("state_stride", c_int64), ("conv_off", c_int64), ("seq_first_row", c_void_p),
+                ("seq_slot", c_void_p), ("channels", c_int32), ("N", c_int32), ("taps", c_int32)]
+
+
 class SampleIOArg(Structure):
     """Mirror of `struct SampleIO` in sampling.cu."""
     _fields_ = [("logits", c_void_p), ("temperature", c_void_p), ("top_p", c_void_p), ("seed", c_void_p),
@@ -85,7 +93,11 @@ _SIGNATURES = {
     "x0ne_add_normed_rmsnorm": [_P, _P, _P, _F, _P, _P, _I, _P, _I, _I, _F, _P],
     "x0ne_whole_norm_rope_kv_write": [_P, _I, _I, _I, _I, _P, _P, _F, _P, _I, _P, _I, _P, _I, None, _P, _P, _I, _I, _P],
     "x0ne_relu2": [_P, _P, _I, _L, _P],
-    "x0ne_moe_route": [_P, _I, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P],
+    "x0ne_moe_route": [_P, _I, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P],
+    "x0ne_rope_pairs_kv_write": [_P, _I, _I, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P, _I, _I, None, _P, _P, _I, _I, _P],
+    "x0ne_diff_heads": [_P, _P, _L, _P, _I, _I, _I, _I, _F, _F, _F, _P],
+    "x0ne_causal_conv_silu": [_P, _L, _I, _P, _P, _P, _L, _L, _P, _P, _P, _I, _I, _I, _P],
+    "x0ne_selective_scan": ["ssm", _I, _I, _P],
     "x0ne_add2_group_rmsnorm": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _P],
     "x0ne_open_pass": [_P, _P, _I, _P, _I, _P, _F, _P, _I, _I, _I, _P],
     "x0ne_head_norm_kv_write": [_P, _I, _I, _I, _I, _P, _P, _F, _F, _I, _I, _P, _I, None, _P, _P, _I, _P],
@@ -136,7 +148,7 @@ def _lib(name: str) -> ctypes.CDLL:
             fn = getattr(lib, fn_name, None)
             if fn is not None:
                 # None: the cache view, by value; "io": the sampler's arguments, by value
-                fn.argtypes = [PagedCacheArg if a is None else SampleIOArg if a == "io" else AttnExtraArg if a == "ex" else a
+                fn.argtypes = [PagedCacheArg if a is None else SampleIOArg if a == "io" else AttnExtraArg if a == "ex" else SsmArg if a == "ssm" else a
                                for a in args]
                 fn.restype = c_int
         _libs[name] = lib
@@ -355,22 +367,30 @@ def moe_tc_takes(dtype: torch.dtype, pairs: int, *widths: int) -> bool:
 
 def moe_route(z: torch.Tensor, correction: torch.Tensor, n: int, groups: int, keep: int, top: int, n_rows: int,
               chosen: torch.Tensor, weights: torch.Tensor, sgate: Optional[torch.Tensor] = None, sg_col: int = 0,
-              on_logits: bool = False) -> None:
+              on_logits: bool = False, sigmoid: bool = False, group_top: int = 1, normalize: bool = False,
+              weight_scale: float = 1.0) -> None:
     """The router's choice per row from float32 logits z [rows, >= n] (see moe.cu): `chosen` int32 [rows, top],
     `weights` float32 [rows, top]; `sgate` float32 [rows] = sigmoid(z[:, sg_col]).  `on_logits`: the choice is made on
-    z + correction itself (no softmax over all outputs) and the weights are the softmax over the chosen values."""
+    z + correction itself (no softmax over all outputs) and the weights are the softmax over the chosen values.
+    `sigmoid`: the scores are sigmoid(z) (`correction` may be None).  `group_top`: a group is worth the sum of that many
+    of its largest values.  `normalize`: the chosen weights are divided by their sum (+ 1e-20) and multiplied by
+    `weight_scale`."""
     lib = _lib("core")
     _need(z, torch.float32, "router logits")
-    _need(correction, torch.float32, "router correction")
+    if correction is not None:
+        _need(correction, torch.float32, "router correction")
+    elif not sigmoid:
+        raise KernelError("moe_route: only a router that scores with the sigmoid goes without a correction")
     _need(chosen, torch.int32, "chosen experts")
     _need(weights, torch.float32, "choice weights")
     if sgate is not None:
         _need(sgate, torch.float32, "shared gate")
-    if correction.numel() != n or z.numel() < n_rows * z.shape[-1] or chosen.numel() < n_rows * top or weights.numel() < n_rows * top \
+    if (correction is not None and correction.numel() != n) or z.numel() < n_rows * z.shape[-1] or chosen.numel() < n_rows * top or weights.numel() < n_rows * top \
             or (sgate is not None and sgate.numel() < n_rows):
         raise KernelError("moe_route: buffers do not match the rows and choices asked for")
     _check(lib, lib.x0ne_moe_route(_ptr(z), z.shape[-1], _ptr(correction), n, groups, keep, top, n_rows, _ptr(chosen),
-                                   _ptr(weights), _ptr(sgate), sg_col, 1 if on_logits else 0, _stream()), "moe_route")
+                                   _ptr(weights), _ptr(sgate), sg_col, 2 if sigmoid else 1 if on_logits else 0, int(group_top),
+                                   1 if normalize else 0, float(weight_scale), _stream()), "moe_route")
 
 
 def moe_group(chosen: torch.Tensor, pairs: int, experts: int, offsets: torch.Tensor, listed: torch.Tensor,
@@ -1202,3 +1222,93 @@ def tanh_rows(x: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
     if out.shape[-1] != x.shape[-1] or x.numel() < n_rows * x.shape[-1] or out.numel() < n_rows * x.shape[-1]:
         raise KernelError("tanh_rows: shapes do not match")
     _check(lib, lib.x0ne_tanh_rows(_ptr(x), _ptr(out), dtype_tag(out.dtype), n_rows * x.shape[-1], _stream()), "tanh_rows")
+
+
+def rope_pairs_kv_write(src: torch.Tensor, k_col: int, v_col: int, freq: Optional[torch.Tensor], table: Optional[torch.Tensor], rot: int,
+                        maps: int, dim: int, unit_eps: Optional[float], q_out: torch.Tensor, q_heads: int, q_padded: bool,
+                        cache: PagedCacheArg, row_slot: torch.Tensor, row_pos: torch.Tensor, n_rows: int, write_kv: bool = True) -> None:
+    """Queries (columns from 0), keys (from k_col) and values (from v_col) of the packed projection `src`: of every
+    (head, map) of `dim` values the first `rot` turn as interleaved pairs by pos * freq[i] (`table`: float32
+    [positions, rot], cosines then sines), then, with `unit_eps` not None, it is divided by its root mean square; queries
+    to q_out ([rows, q_heads * maps, dim], or with `q_padded` [rows, q_heads * maps, maps * dim] with zeros beside the
+    query's own map), keys (a kv head's maps side by side) and values to the pages."""
+    lib = _lib("core")
+    _need(src, src.dtype, "projection")
+    _need(q_out, src.dtype, "queries")
+    if freq is not None:
+        _need(freq, torch.float32, "rotary frequencies")
+    if table is not None:
+        _need(table, torch.float32, "rotary table")
+        if table.dim() != 2 or table.shape[1] != rot:
+            raise KernelError("rope_pairs_kv_write: the table's rows do not hold rot values")
+    if rot and (freq is None or freq.numel() < rot // 2):
+        raise KernelError("rope_pairs_kv_write: fewer frequencies than pairs")
+    q_width = q_heads * maps * (maps * dim if q_padded else dim)
+    if src.numel() < n_rows * src.shape[-1] or q_out.shape[-1] != q_width or q_out.numel() < n_rows * q_width:
+        raise KernelError("rope_pairs_kv_write: buffers smaller than the rows asked for")
+    _check(lib, lib.x0ne_rope_pairs_kv_write(_ptr(src), dtype_tag(src.dtype), src.shape[-1], k_col, v_col, _ptr(freq), _ptr(table),
+                                             0 if table is None else table.shape[0], rot, maps, dim,
+                                             -1.0 if unit_eps is None else float(unit_eps), _ptr(q_out), q_heads, 1 if q_padded else 0,
+                                             cache, _ptr(row_slot), _ptr(row_pos), n_rows, 1 if write_kv else 0, _stream()),
+           "rope_pairs_kv_write")
+
+
+def diff_heads(att: torch.Tensor, gate: Optional[torch.Tensor], gate_ld: int, out: torch.Tensor, n_rows: int, heads: int, vd: int,
+               lam: float, eps: float, post: float) -> None:
+    """out[row, head] = o / sqrt(mean(o^2) + eps) * post * sigmoid(gate[row, head]) with o = a1 - lam * a2, where att
+    holds [rows, heads, 2, vd] (the two maps' results of each head) and `gate` is a view whose row r starts gate_ld
+    values after row r - 1 (None: no gate)."""
+    lib = _lib("core")
+    _need(att, att.dtype, "attention maps")
+    _need(out, att.dtype, "combined heads")
+    if att.shape[-1] != 2 * heads * vd or out.shape[-1] != heads * vd or att.numel() < n_rows * att.shape[-1] or out.numel() < n_rows * heads * vd:
+        raise KernelError("diff_heads: shapes do not match")
+    if gate is not None and (gate.dtype != att.dtype or not gate.is_cuda):
+        raise KernelError("diff_heads: the gate is not of the maps' type")
+    _check(lib, lib.x0ne_diff_heads(_ptr(att), _ptr(gate), int(gate_ld), _ptr(out), dtype_tag(att.dtype), n_rows, heads, vd, float(lam),
+                                    float(eps), float(post), _stream()), "diff_heads")
+
+
+def causal_conv_silu(xz: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, conv_off: int, out: torch.Tensor,
+                     row_slot: torch.Tensor, row_pos: torch.Tensor, n_rows: int, channels: int) -> None:
+    """out[t, c] = silu(bias[c] + sum_k w[c, k] x[t - (K - 1 - k), c]) over the first `channels` columns of xz; inputs ahead of
+    a row are the rows above it while they continue its sequence, then the K - 1 inputs its state row keeps at
+    conv_off (float32 [K - 1, channels], oldest first).  The state is only read."""
+    lib = _lib("core")
+    _need(xz, xz.dtype, "convolution input")
+    _need(out, xz.dtype, "convolution output")
+    _need(w, torch.float32, "convolution taps")
+    _need(state, torch.float32, "state")
+    if bias is not None:
+        _need(bias, torch.float32, "convolution bias")
+    if w.dim() != 2 or w.shape[0] != channels or out.shape[-1] != channels or xz.shape[-1] < channels or state.dim() != 2 \
+            or out.numel() < n_rows * channels or xz.numel() < n_rows * xz.shape[-1]:
+        raise KernelError("causal_conv_silu: shapes do not match")
+    _check(lib, lib.x0ne_causal_conv_silu(_ptr(xz), xz.shape[-1], dtype_tag(xz.dtype), _ptr(w), _ptr(bias), _ptr(state), state.stride(0),
+                                          int(conv_off), _ptr(out), _ptr(row_slot), _ptr(row_pos), n_rows, channels, w.shape[1],
+                                          _stream()), "causal_conv_silu")
+
+
+def selective_scan(u: torch.Tensor, xz: torch.Tensor, z_col: int, dt_raw: torch.Tensor, dt_bias: Optional[torch.Tensor], A: torch.Tensor,
+                   bc: torch.Tensor, b_col: int, c_col: int, D: Optional[torch.Tensor], out: torch.Tensor, state: torch.Tensor,
+                   conv_off: int, taps: int, seq_first_row: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int) -> None:
+    """Per sequence and channel, token by token over the sequence's rows, from and into its state row (S [channels, N] at
+    0, the convolution's last taps - 1 inputs at conv_off): dt = softplus(dt_raw + dt_bias); S = exp(dt A) S + dt u B;
+    out = (S . C + D u) * silu(z).  u, xz (the convolution's input at column 0, z at z_col) and out in the activation type;
+    dt_raw, A (negative), bc (B at b_col, C at c_col), D, state float32."""
+    lib = _lib("core")
+    for t, what in ((u, "scan input"), (xz, "projection"), (out, "scan output")):
+        _need(t, u.dtype, what)
+    for t, what in ((dt_raw, "step sizes"), (A, "decay rates"), (bc, "B and C"), (state, "state")):
+        _need(t, torch.float32, what)
+    for t, what in ((dt_bias, "step size bias"), (D, "skip weights")):
+        if t is not None:
+            _need(t, torch.float32, what)
+    channels, N = A.shape
+    if u.shape[-1] != channels or out.shape[-1] != channels or dt_raw.shape[-1] != channels or state.dim() != 2 \
+            or (dt_bias is not None and dt_bias.numel() != channels) or (D is not None and D.numel() != channels):
+        raise KernelError("selective_scan: shapes do not match")
+    arg = SsmArg(_ptr(u), _ptr(xz), xz.shape[-1], int(z_col), _ptr(dt_raw), _ptr(dt_bias), _ptr(A), _ptr(bc), bc.shape[-1], int(b_col),
+                 int(c_col), _ptr(D), _ptr(out), _ptr(state), state.stride(0), int(conv_off), _ptr(seq_first_row), _ptr(seq_slot),
+                 int(channels), int(N), int(taps))
+    _check(lib, lib.x0ne_selective_scan(arg, dtype_tag(u.dtype), n_seqs, _stream()), "selective_scan")

@@ -1,0 +1,281 @@
+// A selective state-space mixer's two kernels: the short causal convolution with its activation, and the scan.
+//
+// Per sequence and channel c the mixer keeps, in a float32 state row [slots][stride]:
+//   S[c][n], n < N          at c * N + n                       the recurrence's state
+//   the last K - 1 inputs   at conv_off + i * channels + c     of the convolution, oldest first (i = 0 .. K - 2)
+// Both are zero when a sequence starts, so a tap that reaches before the first token meets a zero.
+//
+//   conv:  u[t][c] = silu(bias[c] + sum_k w[c][k] x[t - (K - 1 - k)][c])      (the last column of w meets the current token)
+//   scan:  dt = softplus(dt_raw[t][c] + dt_bias[c])
+//          S[c][n] = exp(dt A[c][n]) S[c][n] + dt u[t][c] B[t][n]
+//          y[t][c] = (sum_n S[c][n] C[t][n] + D[c] u[t][c]) * silu(z[t][c])
+//
+// Step sizes, decays, states and every sum are float32 whatever the activation type.  One device function makes a token's
+// step, for prompts and for one-token steps alike, and the sums over n run in an order that depends on N only (a thread's
+// own states in ascending order, then the threads of a channel as a shuffle tree), so a token's result is the same bits
+// however its sequence was cut into passes and whatever else the pass holds.
+#include "common.cuh"
+
+#define SSM_SPLIT 4        // threads that share a channel's states
+#define SSM_CH 32          // channels per block
+#define SSM_TC 16          // tokens staged at a time
+#define SSM_MAX_TAPS 16
+
+// exp(a * b) for a * b <= 0, closer than the library's exponential (whose error of up to two units in the last place, met
+// again at every token, is what a slowly decaying state adds up): the product's own rounding error is carried along
+// (x_lo), x = n ln2 + r with ln2 in two parts, and exp(r) is a polynomial of degree 7 over |r| <= ln2 / 2, all in fused
+// multiply-adds.  Below 2^-126 the result is zero.
+__device__ __forceinline__ float ssm_exp_prod(float a, float b) {
+    const float x = a * b;
+    const float x_lo = fmaf(a, b, -x);
+    const float n = rintf(x * 1.4426950408889634f);
+    if (n < -126.f) return 0.f;
+    float r = fmaf(n, -0.693145751953125f, x);           // ln2's leading bits: n times it is exact
+    r = fmaf(n, -1.428606765330187e-06f, r) + x_lo;
+    float p = 1.98412698e-4f;                             // 1/7!
+    p = fmaf(p, r, 1.38888889e-3f);
+    p = fmaf(p, r, 8.33333333e-3f);
+    p = fmaf(p, r, 4.16666667e-2f);
+    p = fmaf(p, r, 1.66666667e-1f);
+    p = fmaf(p, r, 0.5f);
+    p = fmaf(p, r, 1.0f);
+    p = fmaf(p, r, 1.0f);
+    return p * __int_as_float(((int)n + 127) << 23);
+}
+
+__device__ __forceinline__ float ssm_silu(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float ssm_softplus(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+// ----------------------------------------------------------------------------------------
+// Convolution.  One thread per (row, channel).  The inputs before a row are the rows above it in the pass while they
+// belong to the same sequence (same slot, positions that count down by one), and the sequence's kept inputs beyond.
+// The state is only read here: the scan, which runs later in the stream, leaves the new last inputs.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void causal_conv_silu_kernel(const T* __restrict__ x, int64_t ld, const float* __restrict__ w, const float* __restrict__ bias,
+                                        const float* __restrict__ state, int64_t state_stride, int64_t conv_off, T* __restrict__ out,
+                                        const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos, int n_rows,
+                                        int channels, int taps) {
+    pdl_launch_dependents();
+    const int64_t item = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int row = (int)(item / channels), c = (int)(item % channels);
+    float wk[SSM_MAX_TAPS];
+    float b = 0.f;
+    if (row < n_rows) {
+#pragma unroll
+        for (int k = 0; k < SSM_MAX_TAPS; ++k) wk[k] = k < taps ? w[(int64_t)c * taps + k] : 0.f;
+        b = bias != nullptr ? bias[c] : 0.f;
+    }
+    pdl_wait();
+    if (row >= n_rows) return;
+    const int slot = row_slot[row], pos = row_pos[row];
+    // how many rows right above this one continue its sequence (at most K - 1 are looked at)
+    int above = 0;
+    while (above < taps - 1 && row - above - 1 >= 0 && row_slot[row - above - 1] == slot && row_pos[row - above - 1] == pos - above - 1) ++above;
+    float acc = b;
+#pragma unroll
+    for (int k = 0; k < SSM_MAX_TAPS; ++k) {
+        if (k >= taps) break;
+        const int back = taps - 1 - k;          // this tap meets the input `back` tokens ago
+        float v = 0.f;
+        if (back <= above) v = to_f32(x[(int64_t)(row - back) * ld + c]);
+        else if (slot >= 0) v = state[(int64_t)slot * state_stride + conv_off + (int64_t)(taps - 1 + above - back) * channels + c];
+        acc = fmaf(wk[k], v, acc);
+    }
+    out[(int64_t)row * channels + c] = from_f32<T>(ssm_silu(acc));
+}
+
+X0NE_API int x0ne_causal_conv_silu(const void* x, int64_t ld, int dt, const float* w, const float* bias, const float* state,
+                                   int64_t state_stride, int64_t conv_off, void* out, const int32_t* row_slot, const int32_t* row_pos,
+                                   int n_rows, int channels, int taps, cudaStream_t stream) {
+    X0NE_REQUIRE(n_rows >= 0 && channels > 0 && taps >= 1 && taps <= SSM_MAX_TAPS && ld >= channels,
+                 "causal_conv: rows %d channels %d taps %d (at most %d)", n_rows, channels, taps, SSM_MAX_TAPS);
+    X0NE_REQUIRE(conv_off >= 0 && state_stride >= conv_off + (int64_t)(taps - 1) * channels, "causal_conv: the state row is too short");
+    if (n_rows == 0) return 0;
+    const int64_t items = (int64_t)n_rows * channels;
+    const dim3 grid((unsigned)((items + 255) / 256));
+    if (dt == X0NE_F32)
+        x0ne_launch(causal_conv_silu_kernel<float>, grid, dim3(256), 0, stream, (const float*)x, ld, w, bias, state, state_stride, conv_off,
+                    (float*)out, row_slot, row_pos, n_rows, channels, taps);
+    else if (dt == X0NE_BF16)
+        x0ne_launch(causal_conv_silu_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)x, ld, w, bias, state, state_stride, conv_off,
+                    (bf16*)out, row_slot, row_pos, n_rows, channels, taps);
+    else
+        X0NE_REQUIRE(false, "causal_conv: unknown dtype tag %d", dt);
+    X0NE_LAUNCH_CHECK();
+}
+
+// ----------------------------------------------------------------------------------------
+// Scan.  A block takes one sequence and SSM_CH channels; SSM_SPLIT threads share a channel, each with NS states
+// (n = part * NS + i) in registers.  The sequence's rows are staged SSM_TC at a time: all threads fetch the next tokens'
+// values into registers while the block works through the staged ones, then turn them into what the step needs
+// (softplus, silu) on their way to shared memory.  Only S is carried from token to token.
+// ----------------------------------------------------------------------------------------
+struct SsmArgs {
+    const void* u;            // [rows][channels], activation type: the convolution's output
+    const void* xz;           // [rows][xz_ld], activation type: the convolution's input at column 0, z at column z_col
+    int64_t xz_ld;
+    int32_t z_col;
+    const float* dt_raw;      // [rows][channels]
+    const float* dt_bias;     // [channels] or null
+    const float* A;           // [channels][N], negative
+    const float* bc;          // [rows][bc_ld]: B at b_col, C at c_col
+    int64_t bc_ld;
+    int32_t b_col, c_col;
+    const float* D;           // [channels] or null
+    void* out;                // [rows][channels], activation type
+    float* state;
+    int64_t state_stride, conv_off;
+    const int32_t* seq_first_row;
+    const int32_t* seq_slot;
+    int32_t channels, N, taps;
+};
+
+template <typename T, int NS>
+__global__ void __launch_bounds__(SSM_CH * SSM_SPLIT) selective_scan_kernel(SsmArgs a) {
+    constexpr int THREADS = SSM_CH * SSM_SPLIT;
+    constexpr int NP = NS * SSM_SPLIT;                          // states per channel as the block holds them
+    constexpr int PER_CH = SSM_TC * SSM_CH / THREADS;           // staged (token, channel) values per thread
+    constexpr int PER_N = (SSM_TC * NP + THREADS - 1) / THREADS;
+    __shared__ float s_dt[SSM_TC][SSM_CH], s_u[SSM_TC][SSM_CH], s_z[SSM_TC][SSM_CH];
+    __shared__ float s_b[SSM_TC][NP], s_c[SSM_TC][NP];
+    pdl_launch_dependents();
+    const int tid = threadIdx.x;
+    const int cl = tid / SSM_SPLIT, part = tid % SSM_SPLIT;
+    const int c = blockIdx.x * SSM_CH + cl;
+    const int seq = blockIdx.y;
+    const bool live = c < a.channels;
+    float An[NS], S[NS];
+    float dtb = 0.f, Dc = 0.f;
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+        const int n = part * NS + i;
+        An[i] = live && n < a.N ? a.A[(int64_t)c * a.N + n] : 0.f;
+    }
+    if (live) {
+        dtb = a.dt_bias != nullptr ? a.dt_bias[c] : 0.f;
+        Dc = a.D != nullptr ? a.D[c] : 0.f;
+    }
+    // the staging thread's own (token, channel) and (token, n) places
+    const int c_st = tid % SSM_CH, ch_st = blockIdx.x * SSM_CH + c_st;
+    const float dtb_st = ch_st < a.channels && a.dt_bias != nullptr ? a.dt_bias[ch_st] : 0.f;
+    pdl_wait();
+    const int slot = a.seq_slot[seq];
+    const int row0 = a.seq_first_row[seq], n_tok = a.seq_first_row[seq + 1] - row0;
+    if (slot < 0 || n_tok <= 0) return;
+    float* st = a.state + (int64_t)slot * a.state_stride;
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+        const int n = part * NS + i;
+        S[i] = live && n < a.N ? st[(int64_t)c * a.N + n] : 0.f;
+    }
+    const T* u = (const T*)a.u;
+    const T* xz = (const T*)a.xz;
+    T* out = (T*)a.out;
+
+    float f_dt[PER_CH], f_u[PER_CH], f_z[PER_CH], f_b[PER_N], f_c[PER_N];
+    auto fetch = [&](int t0) {
+#pragma unroll
+        for (int j = 0; j < PER_CH; ++j) {
+            const int t = t0 + (tid / SSM_CH) + j * (THREADS / SSM_CH);
+            const bool ok = t < n_tok && ch_st < a.channels;
+            const int64_t r = row0 + (ok ? t : 0);
+            f_dt[j] = ok ? a.dt_raw[r * a.channels + ch_st] : 0.f;
+            f_u[j] = ok ? to_f32(u[r * a.channels + ch_st]) : 0.f;
+            f_z[j] = ok ? to_f32(xz[r * a.xz_ld + a.z_col + ch_st]) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < PER_N; ++j) {
+            const int e = tid + j * THREADS;
+            const int t = t0 + e / NP, n = e % NP;
+            const bool ok = e < SSM_TC * NP && t < n_tok && n < a.N;
+            const int64_t r = row0 + (ok ? t : 0);
+            f_b[j] = ok ? a.bc[r * a.bc_ld + a.b_col + n] : 0.f;
+            f_c[j] = ok ? a.bc[r * a.bc_ld + a.c_col + n] : 0.f;
+        }
+    };
+    fetch(0);
+    for (int t0 = 0; t0 < n_tok; t0 += SSM_TC) {
+#pragma unroll
+        for (int j = 0; j < PER_CH; ++j) {
+            const int tl = (tid / SSM_CH) + j * (THREADS / SSM_CH);
+            s_dt[tl][c_st] = ssm_softplus(f_dt[j] + dtb_st);
+            s_u[tl][c_st] = f_u[j];
+            s_z[tl][c_st] = ssm_silu(f_z[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < PER_N; ++j) {
+            const int e = tid + j * THREADS;
+            if (e < SSM_TC * NP) {
+                s_b[e / NP][e % NP] = f_b[j];
+                s_c[e / NP][e % NP] = f_c[j];
+            }
+        }
+        __syncthreads();
+        if (t0 + SSM_TC < n_tok) fetch(t0 + SSM_TC);
+        const int nt = min(SSM_TC, n_tok - t0);
+        for (int tl = 0; tl < nt; ++tl) {
+            const float dt = s_dt[tl][cl], uv = s_u[tl][cl];
+            const float dtu = dt * uv;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < NS; ++i) {
+                S[i] = fmaf(ssm_exp_prod(dt, An[i]), S[i], dtu * s_b[tl][part * NS + i]);
+                acc = fmaf(S[i], s_c[tl][part * NS + i], acc);
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (part == 0 && live) out[(int64_t)(row0 + t0 + tl) * a.channels + c] = from_f32<T>(fmaf(Dc, uv, acc) * s_z[tl][cl]);
+        }
+        __syncthreads();
+    }
+    if (!live) return;
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+        const int n = part * NS + i;
+        if (n < a.N) st[(int64_t)c * a.N + n] = S[i];
+    }
+    if (part == 0 && a.taps > 1) {
+        // the last K - 1 inputs of the convolution: rows of this pass, and, where the pass brought fewer, the kept ones moved up
+        float keep[SSM_MAX_TAPS];
+        const int kept = a.taps - 1;
+#pragma unroll
+        for (int i = 0; i < SSM_MAX_TAPS; ++i) {
+            if (i >= kept) break;
+            const int t = n_tok - kept + i;         // the token of this pass that belongs at place i (negative: an older one)
+            keep[i] = t >= 0 ? to_f32(xz[(int64_t)(row0 + t) * a.xz_ld + c]) : st[a.conv_off + (int64_t)(i + n_tok) * a.channels + c];
+        }
+#pragma unroll
+        for (int i = 0; i < SSM_MAX_TAPS; ++i) {
+            if (i >= kept) break;
+            st[a.conv_off + (int64_t)i * a.channels + c] = keep[i];
+        }
+    }
+}
+
+template <typename T>
+static int selective_scan_launch(const SsmArgs& a, int n_seqs, cudaStream_t stream) {
+    const dim3 grid((unsigned)((a.channels + SSM_CH - 1) / SSM_CH), (unsigned)n_seqs), block(SSM_CH * SSM_SPLIT);
+    const int ns = (a.N + SSM_SPLIT - 1) / SSM_SPLIT;
+    if (ns <= 1) x0ne_launch(selective_scan_kernel<T, 1>, grid, block, 0, stream, a);
+    else if (ns <= 2) x0ne_launch(selective_scan_kernel<T, 2>, grid, block, 0, stream, a);
+    else if (ns <= 4) x0ne_launch(selective_scan_kernel<T, 4>, grid, block, 0, stream, a);
+    else if (ns <= 6) x0ne_launch(selective_scan_kernel<T, 6>, grid, block, 0, stream, a);
+    else if (ns <= 8) x0ne_launch(selective_scan_kernel<T, 8>, grid, block, 0, stream, a);
+    else if (ns <= 16) x0ne_launch(selective_scan_kernel<T, 16>, grid, block, 0, stream, a);
+    else x0ne_launch(selective_scan_kernel<T, 32>, grid, block, 0, stream, a);
+    X0NE_LAUNCH_CHECK();
+}
+
+X0NE_API int x0ne_selective_scan(SsmArgs a, int dt, int n_seqs, cudaStream_t stream) {
+    X0NE_REQUIRE(n_seqs >= 0 && n_seqs <= 65535 && a.channels > 0 && a.N > 0 && a.N <= 32 * SSM_SPLIT && a.taps >= 1 && a.taps <= SSM_MAX_TAPS,
+                 "selective_scan: %d sequences, %d channels of %d states (at most %d), %d taps", n_seqs, a.channels, a.N, 32 * SSM_SPLIT, a.taps);
+    X0NE_REQUIRE(a.conv_off >= (int64_t)a.channels * a.N && a.state_stride >= a.conv_off + (int64_t)(a.taps - 1) * a.channels,
+                 "selective_scan: the state row is too short");
+    X0NE_REQUIRE(a.xz_ld >= a.channels && a.z_col >= 0 && a.z_col + a.channels <= a.xz_ld && a.b_col >= 0 && a.c_col >= 0 &&
+                     a.b_col + a.N <= a.bc_ld && a.c_col + a.N <= a.bc_ld, "selective_scan: columns lie outside their rows");
+    if (n_seqs == 0) return 0;
+    if (dt == X0NE_F32) return selective_scan_launch<float>(a, n_seqs, stream);
+    if (dt == X0NE_BF16) return selective_scan_launch<bf16>(a, n_seqs, stream);
+    X0NE_REQUIRE(false, "selective_scan: unknown dtype tag %d", dt);
+}

@@ -14,11 +14,16 @@ from .linear import Linear
 
 
 class MaskedAttention(Mixer):
-    """q, k, v from one product on the packed [q; k; v] weight; no rotation; keys of `head_dim` and
+    """q, k, v from one product on the packed [q; k; v] weight; keys of `head_dim` and
     values of `v_dim` per kv head written to the cache; softmax attention of every query over the
     keys j <= i it may see: all of them, the last `window`, or (with `chunk` = c) those with
     floor(j / c) = floor(i / c), chunks counted from the sequence's first position; q head h reads kv
     head h // (q_heads // kv_heads); output projection.
+
+    Without `position` nothing is rotated.  With it (the name of a position encoding of the model whose pairs are
+    interleaved) queries and keys turn by their positions, and with `qk_unit_eps` each head's query and key is then
+    divided by its root mean square (no weight).  `sink_zero` adds one term of score zero to every softmax
+    denominator: exp(s_j) / (1 + sum exp(s)).
 
     Value blending (`v_blend`): the first layer of a model that says "source" keeps its values of the
     pass's rows; a layer that says "blend" replaces its own by (1 - a) v + a v_source with its learned
@@ -26,7 +31,7 @@ class MaskedAttention(Mixer):
     source's kv_heads x v_dim.
 
     Parameters: hidden_size, q_heads, kv_heads, head_dim, v_dim, scale, chunk (None: no chunks), window
-    (None: all keys), v_blend (None | "source" | "blend"), names.{q, k, v, o, v_blend}.
+    (None: all keys), v_blend (None | "source" | "blend"), position, qk_unit_eps, sink_zero, names.{q, k, v, o, v_blend}.
     """
     replayable = True
 
@@ -46,6 +51,15 @@ class MaskedAttention(Mixer):
         self.v_blend = g("v_blend")
         if self.v_blend not in (None, "source", "blend"):
             raise ValueError(f"v_blend {self.v_blend!r} is not None, 'source' or 'blend'")
+        pos = g("position")
+        self.position = env.positions[pos] if pos is not None else None
+        if self.position is not None and getattr(self.position, "layout", None) != "interleaved":
+            raise ValueError("this attention rotates interleaved pairs; its position encoding has another layout")
+        self.qk_unit_eps = g("qk_unit_eps")
+        self.prepared = self.position is not None or self.qk_unit_eps is not None    # queries and keys change on their way
+        if self.prepared and self.v_blend is not None:
+            raise ValueError("value blending together with rotated or normed queries and keys is not served")
+        self.sink = torch.zeros(self.q_heads, dtype=torch.float32, device=env.device) if g("sink_zero") else None
         self.q_dim = self.q_heads * self.head_dim
         self.k_dim = self.kv_heads * self.head_dim
         self.kv_v_dim = self.kv_heads * self.v_dim
@@ -87,12 +101,23 @@ class MaskedAttention(Mixer):
         out = ctx.ws.buffer("delta", (rows, self.hidden), dt)
         self.qkv(x, qkv, n_rows)
         view = ctx.cache.kv_view(entry if cache_entry is None else cache_entry)
+        if self.prepared:
+            q = ctx.ws.buffer("mattn.q", (rows, self.q_dim), dt)
+            freq, rot = self.position.rotary() if self.position is not None else (None, 0)
+            table = self.position.cos_sin_table(self.env.max_positions) if rot and self.env.max_positions else None
+            ops.rope_pairs_kv_write(qkv, self.q_dim, self.q_dim + self.k_dim, freq, table, rot, 1, self.head_dim,
+                                    None if self.qk_unit_eps is None else float(self.qk_unit_eps), q, self.q_heads, False, view,
+                                    ctx.row_slot, ctx.row_pos, n_rows, write_cache)
+            extra = ops.attn_extra(chunk=self.chunk, sink=self.sink)
+            run_attention_ex(ctx, q, att, view, n_rows, self.q_heads, self.scale, self.window, extra)
+            self.o(att, out, n_rows)
+            return out
         if write_cache:
             mode = {None: 0, "source": 1, "blend": 2}[self.v_blend]
             first = ctx.ws.buffer("mattn.v_source", (rows, self.kv_v_dim), dt) if mode else None
             ops.kv_write_blend(qkv, self.q_dim, self.q_dim + self.k_dim, view, ctx.row_slot, ctx.row_pos, n_rows, mode,
                                first, self.blend)
-        extra = ops.attn_extra(chunk=self.chunk, q_ld=width)
+        extra = ops.attn_extra(chunk=self.chunk, q_ld=width, sink=self.sink)
         run_attention_ex(ctx, qkv, att, view, n_rows, self.q_heads, self.scale, self.window, extra)
         self.o(att, out, n_rows)
         return out

@@ -10,6 +10,7 @@ from ..csrc import ops
 from ..weights.loader import TensorNeed
 from .base import FEED_FORWARDS, FeedForward
 from .linear import Linear
+from .mlp import SwiGLU
 
 
 class RoutedExperts(FeedForward):
@@ -21,11 +22,16 @@ class RoutedExperts(FeedForward):
     those the `top` largest values are chosen; the weights are the chosen outputs' scores s, not
     renormalized.  With `choice` "logits" there is no softmax over all outputs: the `top` largest z + correction (the
     correction is then the router's bias) are chosen and the weights are the softmax over the chosen values alone.
+    With `choice` "sigmoid" the scores are s = sigmoid(z), each output by itself; the choice is made on s (+ correction,
+    if the model has one) and the weights are the chosen scores.  For every kind of choice a group may be worth the sum
+    of its `group_top` largest values instead of the largest one, and with `normalize` the chosen weights are divided
+    by their sum (+ 1e-20) and multiplied by `weight_scale`.
     An expert is down(act(up x)) with act the squared ReLU, or, with `activation` "swiglu",
     down(silu(gate x) * up x) (gate and up packed per expert, gate rows first); no biases.  The last
     `identity` router outputs are identity experts: they return x itself and have no tensors.  The
     shared expert has the same form with a width of its own, runs for every row, and is multiplied
-    by the sigmoid of one more projection of x (`shared_gate`).
+    by the sigmoid of one more projection of x (`shared_gate`; without it the shared expert is added as it is).  Beside
+    gated experts the shared expert is gated too (names.shared_gate_proj is its gate matrix).
 
     One product gives the router logits and the shared gate's logit (float32); a kernel makes the
     choice; the (row, choice) pairs are listed expert by expert on the device and both products of the
@@ -34,8 +40,9 @@ class RoutedExperts(FeedForward):
     the choices.
 
     Parameters: hidden_size, experts, identity, top, groups, keep_groups, expert_size, activation
-    ("relu2" | "swiglu"), choice ("scores" | "logits"), shared_size (None: no shared expert), shared_gate,
-    names.{router, correction, gate, up, down (patterns with {e}), shared_up, shared_down, shared_gate}.
+    ("relu2" | "swiglu"), choice ("scores" | "logits" | "sigmoid"), group_top (default 1), normalize, weight_scale,
+    shared_size (None: no shared expert), shared_gate, names.{router, correction (may be absent with "sigmoid"), gate,
+    up, down (patterns with {e}), shared_up, shared_down, shared_gate, shared_gate_proj}.
     """
     replayable = True
 
@@ -58,10 +65,24 @@ class RoutedExperts(FeedForward):
         self.gated = self.activation == "swiglu"
         self.pair_block = 0
         self.choice = g("choice", "scores") or "scores"
-        if self.choice not in ("scores", "logits"):
-            raise ValueError(f"router choice {self.choice!r} is not served; served: 'scores', 'logits'")
+        if self.choice not in ("scores", "logits", "sigmoid"):
+            raise ValueError(f"router choice {self.choice!r} is not served; served: 'scores', 'logits', 'sigmoid'")
+        self.group_top = int(g("group_top") or 1)
+        self.normalize = bool(g("normalize"))
+        self.weight_scale = float(g("weight_scale", 1.0) if g("weight_scale") is not None else 1.0)
+        self.has_correction = spec["names"].get("correction") is not None
+        if not self.has_correction and self.choice != "sigmoid":
+            raise ValueError("only a router that scores with the sigmoid goes without a correction")
+        if self.group_top < 1:
+            raise ValueError("a group is worth the sum of at least one of its values")
+        self.shared_glu = None
         if self.gated and self.shared_size:
-            raise ValueError("a shared expert beside gated experts is not served")
+            if self.shared_gate:
+                raise ValueError("a gate on the shared expert beside gated experts is not served")
+            n = spec["names"]
+            self.shared_glu = SwiGLU(PartSpec("swiglu", dict(hidden_size=self.hidden, intermediate_size=self.shared_size,
+                                                            names=dict(gate=n["shared_gate_proj"], up=n["shared_up"], down=n["shared_down"]))), env)
+            self.shared_glu.out_buffer = "moe.shared_out"
         if self.n_out % self.groups or not 1 <= self.keep_groups <= self.groups or \
                 not 1 <= self.top <= self.keep_groups * (self.n_out // self.groups):
             raise ValueError(f"{self.n_out} router outputs in {self.groups} groups of which {self.keep_groups} stay cannot "
@@ -78,9 +99,13 @@ class RoutedExperts(FeedForward):
             if gated:
                 needs.append(TensorNeed(n["gate"].format(e=e), (ff, h)))
             needs += [TensorNeed(n["up"].format(e=e), (ff, h)), TensorNeed(n["down"].format(e=e), (h, ff))]
-        needs += [TensorNeed(n["router"], (E + I, h)), TensorNeed(n["correction"], (E + I,), role="vector", init="linear")]
+        needs.append(TensorNeed(n["router"], (E + I, h)))
+        if n.get("correction") is not None:
+            needs.append(TensorNeed(n["correction"], (E + I,), role="vector", init="linear"))
         sf = int(spec.get("shared_size") or 0)
-        if sf:
+        if sf and gated:
+            needs += [TensorNeed(n["shared_gate_proj"], (sf, h)), TensorNeed(n["shared_up"], (sf, h)), TensorNeed(n["shared_down"], (h, sf))]
+        elif sf:
             needs += [TensorNeed(n["shared_up"], (sf, h)), TensorNeed(n["shared_down"], (h, sf))]
             if spec.get("shared_gate"):
                 needs.append(TensorNeed(n["shared_gate"], (1, h)))
@@ -90,7 +115,7 @@ class RoutedExperts(FeedForward):
         n = self.spec["names"]
         rows = [tensors[n["router"]]] + ([tensors[n["shared_gate"]]] if self.shared_gate else [])
         self.router = Linear(torch.cat(rows, dim=0).contiguous())
-        self.correction = tensors[n["correction"]]
+        self.correction = tensors[n["correction"]] if self.has_correction else None
         if self.gated:
             # [E, 2 ff, hidden]: an expert's gate rows, then its up rows; where ff is a multiple of MOE_PAIR_BLOCK, in blocks of that
             # many gate rows followed by the up rows of the same outputs, so that a tile of the tensor-core product holds both
@@ -105,7 +130,9 @@ class RoutedExperts(FeedForward):
         else:
             self.up = torch.stack([tensors[n["up"].format(e=e)] for e in range(self.experts)]).contiguous()   # [E, ff, hidden]
         self.down = torch.stack([tensors[n["down"].format(e=e)] for e in range(self.experts)]).contiguous()   # [E, hidden, ff]
-        if self.shared_size:
+        if self.shared_glu is not None:
+            self.shared_glu.bind(tensors)
+        elif self.shared_size:
             self.shared_up = Linear(tensors[n["shared_up"]])
             self.shared_down = Linear(tensors[n["shared_down"]])
 
@@ -113,7 +140,9 @@ class RoutedExperts(FeedForward):
         """The router, the shared expert and every expert: what a step of a batch large enough to reach all experts
         reads (a small batch reads at most rows x top of them)."""
         total = self.router.weight_bytes() + (self.up.numel() + self.down.numel()) * self.up.element_size()
-        if self.shared_size:
+        if self.shared_glu is not None:
+            total += self.shared_glu.weight_bytes()
+        elif self.shared_size:
             total += self.shared_up.weight_bytes() + self.shared_down.weight_bytes()
         return total
 
@@ -133,7 +162,8 @@ class RoutedExperts(FeedForward):
         out = ws.buffer(self.out_buffer, (rows, self.hidden), dt)
         self.router(x, z, n_rows)
         ops.moe_route(z, self.correction, self.n_out, self.groups, self.keep_groups, top, n_rows, chosen, weights, sgate, self.n_out,
-                      on_logits=self.choice == "logits")
+                      on_logits=self.choice == "logits", sigmoid=self.choice == "sigmoid", group_top=self.group_top,
+                      normalize=self.normalize, weight_scale=self.weight_scale)
         pairs = n_rows * top
         up_kind = 2 if self.gated else 0
         if (not self.gated or self.pair_block) and ops.moe_tc_takes(dt, pairs, self.hidden, self.inter):
@@ -151,7 +181,9 @@ class RoutedExperts(FeedForward):
             ops.moe_product(up_kind, x, self.up, listed, tiles, n_tiles, top, act, self.pair_block)
             ops.moe_product(1, act, self.down, listed, tiles, n_tiles, top, y)
         shared = None
-        if self.shared_size:
+        if self.shared_glu is not None:
+            shared = self.shared_glu.forward(ctx, x, n_rows)
+        elif self.shared_size:
             su = ws.buffer("moe.shared_up", (rows, self.shared_size), dt)
             shared = ws.buffer("moe.shared_out", (rows, self.hidden), dt)
             self.shared_up(x, su, n_rows)

@@ -87,7 +87,9 @@ class YarnRope(PositionEncoding):
     i + rotary_dim / 2.  The pair (u, v) at position p becomes (u c - v s, v c + u s) with
     c = mag cos(p f_i), s = mag sin(p f_i).  The rotation runs inside the mixer's kernel; this part
     owns the frequencies and the table.  Parameters: rotary_dim, theta, scaling (None or {factor,
-    original, fast, slow}), layout."""
+    original, fast, slow}), layout, angle_in_float32 (default False: the table's angles are position x
+    frequency in float64; True: the float32 product of the float32 position and frequency, what a kernel
+    that computes the angle itself gets)."""
     replayable = True
     TABLE_POSITIONS = 1 << 16      # the table covers this many positions at most; kernels compute the rest
 
@@ -97,6 +99,7 @@ class YarnRope(PositionEncoding):
         if self.rotary_dim % 2 or self.rotary_dim <= 0:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and positive")
         self.theta = float(spec["theta"])
+        self.angle_in_float32 = bool(spec.get("angle_in_float32"))
         self.layout = spec.get("layout", "interleaved")
         if self.layout not in ("interleaved", "half"):
             raise ValueError(f"rotary layout {self.layout!r} is neither 'interleaved' nor 'half'")
@@ -113,7 +116,10 @@ class YarnRope(PositionEncoding):
         in float64 on the host."""
         positions = max(1, min(int(positions), self.TABLE_POSITIONS))
         if self._cos_sin is None or self._cos_sin.shape[0] < positions:
-            ang = np.arange(positions, dtype=np.float64)[:, None] * self.freq64[None, :]
+            if self.angle_in_float32:
+                ang = (np.arange(positions, dtype=np.float32)[:, None] * self.inv_freq[None, :]).astype(np.float32).astype(np.float64)
+            else:
+                ang = np.arange(positions, dtype=np.float64)[:, None] * self.freq64[None, :]
             tab = (np.concatenate([np.cos(ang), np.sin(ang)], axis=1) * self.mag).astype(np.float32)
             self._cos_sin = torch.from_numpy(tab).to(self.env.device)
         return self._cos_sin
