@@ -181,31 +181,36 @@ def route(z: torch.Tensor, top: int, groups: int, keep: int, scale: float):
     T, E = z.shape
     s = torch.sigmoid(z)
     per = E // groups
+
+    def largest(x, k):
+        """Indices of the k largest values of each row; of equal values the one with the lower index goes first."""
+        return torch.sort(x, dim=-1, descending=True, stable=True).indices[:, :k]
+
     allowed = torch.ones(T, E, dtype=torch.bool)
     if keep < groups:
-        worth = s.reshape(T, groups, per).topk(min(2, per), dim=-1).values.sum(dim=-1)
-        best = worth.topk(keep, dim=-1).indices
+        worth = s.reshape(T, groups, per).sort(dim=-1, descending=True).values[:, :, :2].sum(dim=-1)
         gmask = torch.zeros(T, groups, dtype=torch.bool)
-        gmask.scatter_(1, best, True)
+        gmask.scatter_(1, largest(worth, keep), True)
         allowed = gmask[:, :, None].expand(T, groups, per).reshape(T, E)
-    chosen = s.masked_fill(~allowed, float("-inf")).topk(top, dim=-1).indices
+    chosen = largest(s.masked_fill(~allowed, float("-inf")), top)
     w = s.gather(1, chosen)
     return chosen, w / (w.sum(dim=-1, keepdim=True) + 1e-20) * scale
 
 
 def routed_ffn(h, t: Mapping[str, torch.Tensor], p: str, mlp: Mapping, chosen=None, record=None):
     """`chosen` [T, top]: the experts to take instead of the router's own choice (the weights are still worked out
-    from this function's scores); `record`: a list that receives the choice made."""
+    from this function's scores); `record`: a list that receives the router's own choice."""
     r = mlp["router"]
     groups = (r.get("groups") or {}).get("count", 1)
     keep = (r.get("groups") or {}).get("keep", groups)
     z = h @ f32(t[p + ".router"]).T
-    own, w = route(z, r["top"], groups, keep, float(r.get("scale", 1.0)))
-    if chosen is not None:
-        s = torch.sigmoid(z).gather(1, chosen)
-        own, w = chosen, s / (s.sum(dim=-1, keepdim=True) + 1e-20) * float(r.get("scale", 1.0))
+    scale = float(r["scale"]) if r.get("scale") is not None else 1.0
+    own, w = route(z, r["top"], groups, keep, scale)
     if record is not None:
         record.append(own.clone())
+    if chosen is not None:
+        s = torch.sigmoid(z).gather(1, chosen)
+        own, w = chosen, s / (s.sum(dim=-1, keepdim=True) + 1e-20) * scale
     out = torch.zeros_like(h)
     for e in range(r["experts"]):
         rows, col = (own == e).nonzero(as_tuple=True)

@@ -3,7 +3,7 @@
 // multiple of 16 in shared memory), values that are the leading part of the key rows (a latent
 // cache read by every head), a chunked mask, a sliding window, first keys that stay visible whatever
 // the window, a per-head sink in the softmax denominator, a per-head slope times the distance i - j taken off the
-// scaled score, and a sigmoid gate on the output per (row, head) or per (row, head, value).
+// scaled score, a sigmoid gate on the output per (row, head) or per (row, head, value), and results written as float32.
 //
 // Both kernels are flash attention on `mma.sync` m16n8k16 with float32 accumulation.  Scores,
 // maxima, sums and weights are float32; for the product with the values a weight p is split into
@@ -49,6 +49,12 @@ __device__ __forceinline__ void fx_cp16(bf16* dst, const bf16* src, bool valid) 
 __device__ __forceinline__ void fx_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void fx_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// A result at place i (counted in values) of the output: bfloat16, or float32 for a caller that asked for it.
+__device__ __forceinline__ void fx_store(bf16* out, int64_t i, float v, bool f32) {
+    if (f32) reinterpret_cast<float*>(out)[i] = v;
+    else out[i] = __float2bfloat16_rn(v);
+}
 
 __device__ __forceinline__ uint32_t fx_pack(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -356,8 +362,8 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
     }
     const bf16* ga = (const bf16*)ex.gate + (int64_t)(row0 + r_a) * ex.gate_ld + (int64_t)head * sh.vd;
     const bf16* gb = (const bf16*)ex.gate + (int64_t)(row0 + r_b) * ex.gate_ld + (int64_t)head * sh.vd;
-    bf16* oa = out + ((int64_t)(row0 + r_a) * q_heads + head) * sh.vd;
-    bf16* ob = out + ((int64_t)(row0 + r_b) * q_heads + head) * sh.vd;
+    const int64_t oa = ((int64_t)(row0 + r_a) * q_heads + head) * sh.vd, ob = ((int64_t)(row0 + r_b) * q_heads + head) * sh.vd;
+    const bool f32 = ex.out_f32 > 0;
 #pragma unroll
     for (int n = 0; n < DVT; ++n) {
 #pragma unroll
@@ -365,11 +371,11 @@ flex_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCac
             const int c = 8 * n + 2 * t + e;
             if (c < sh.vd) {
                 if (wide) {
-                    if (ok_a) oa[c] = __float2bfloat16_rn(o[n][e] * f_a * (1.0f / (1.0f + expf(-__bfloat162float(ga[c])))));
-                    if (ok_b) ob[c] = __float2bfloat16_rn(o[n][2 + e] * f_b * (1.0f / (1.0f + expf(-__bfloat162float(gb[c])))));
+                    if (ok_a) fx_store(out, oa + c, o[n][e] * f_a * (1.0f / (1.0f + expf(-__bfloat162float(ga[c])))), f32);
+                    if (ok_b) fx_store(out, ob + c, o[n][2 + e] * f_b * (1.0f / (1.0f + expf(-__bfloat162float(gb[c])))), f32);
                 } else {
-                    if (ok_a) oa[c] = __float2bfloat16_rn(o[n][e] * f_a);
-                    if (ok_b) ob[c] = __float2bfloat16_rn(o[n][2 + e] * f_b);
+                    if (ok_a) fx_store(out, oa + c, o[n][e] * f_a, f32);
+                    if (ok_b) fx_store(out, ob + c, o[n][2 + e] * f_b, f32);
                 }
             }
         }
@@ -553,13 +559,13 @@ flex_decode_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, PagedCach
     const bool wide = ex.gate != nullptr && ex.gate_wide > 0;
     if (ex.gate != nullptr && !wide) fin *= 1.0f / (1.0f + expf(-__bfloat162float(((const bf16*)ex.gate)[(int64_t)row * ex.gate_ld + head])));
     const bf16* gw = (const bf16*)ex.gate + (int64_t)row * ex.gate_ld + (int64_t)head * sh.vd;
-    bf16* orow = out + ((int64_t)row * q_heads + head) * sh.vd;
+    const int64_t orow = ((int64_t)row * q_heads + head) * sh.vd;
     for (int c = c0; c < sh.vd; c += 8) {
         float acc = 0.f;
         for (int w = 0; w < 4; ++w) acc += mg[((int64_t)w * 16 + item) * ps + 2 + c] * f[w];
         acc *= fin;
         if (wide) acc *= 1.0f / (1.0f + expf(-__bfloat162float(gw[c])));
-        orow[c] = __float2bfloat16_rn(acc);
+        fx_store(out, orow + c, acc, ex.out_f32 > 0);
     }
 }
 
@@ -608,7 +614,7 @@ flex_decode_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ o
         }
     }
     __syncthreads();
-    bf16* orow = out + ((int64_t)row * q_heads + head0) * vd;
+    const int64_t orow = ((int64_t)row * q_heads + head0) * vd;
     for (int i = tid; i < n_items * vd; i += 256) {
         const int item = i / vd, c = i - item * vd;
         const float* src = base + (int64_t)item * ps + 2 + c;
@@ -617,7 +623,7 @@ flex_decode_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ o
         acc *= fin_s[item];
         if (ex.gate != nullptr && ex.gate_wide > 0)      // heads head0 .. of the row lie one after the other: value i of them
             acc *= 1.0f / (1.0f + expf(-__bfloat162float(((const bf16*)ex.gate)[(int64_t)row * ex.gate_ld + (int64_t)head0 * vd + i])));
-        orow[i] = __float2bfloat16_rn(acc);
+        fx_store(out, orow + i, acc, ex.out_f32 > 0);
     }
 }
 

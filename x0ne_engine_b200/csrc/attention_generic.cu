@@ -20,7 +20,8 @@
 // value width other than the keys', values read out of the key rows, a per-head sink in the
 // denominator, a sigmoid gate on the output (per (row, head), or per value), a per-head slope times the
 // distance i - j taken off every score, and first keys that stay visible
-// whatever the window (they are taken first, in tiles of 32 from key 0, then the window's).  With none of them asked for the
+// whatever the window (they are taken first, in tiles of 32 from key 0, then the window's), and results written as float32
+// for a caller that goes on in 32-bit.  With none of them asked for the
 // operations and their order are the ones above.
 
 #define ATT_MAX_I 16  // value width <= 32 * ATT_MAX_I
@@ -103,14 +104,20 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, T* __restrict__ o
 #pragma unroll
         for (int i = 0; i < ATT_MAX_I; ++i) acc[i] *= alpha;
     }
-    T* o = out + ((int64_t)row * q_heads + head) * vd;
+    const int64_t o0 = ((int64_t)row * q_heads + head) * vd;
+    T* o = out + o0;
+    float* of = ex.out_f32 > 0 ? reinterpret_cast<float*>(out) + o0 : nullptr;
     float inv = l > 0.f ? 1.0f / l : 0.f;      // a row with no readable key (a padding row) gets zeros
     if (ex.gate != nullptr && ex.gate_wide <= 0) inv *= 1.0f / (1.0f + expf(-to_f32(((const T*)ex.gate)[(int64_t)row * ex.gate_ld + head])));
     const T* gw = ex.gate != nullptr && ex.gate_wide > 0 ? (const T*)ex.gate + (int64_t)row * ex.gate_ld + (int64_t)head * vd : nullptr;
 #pragma unroll
     for (int i = 0; i < ATT_MAX_I; ++i) {
         const int d = lane + 32 * i;
-        if (d < vd) o[d] = from_f32<T>(gw != nullptr ? acc[i] * inv * (1.0f / (1.0f + expf(-to_f32(gw[d])))) : acc[i] * inv);
+        if (d < vd) {
+            const float r = gw != nullptr ? acc[i] * inv * (1.0f / (1.0f + expf(-to_f32(gw[d])))) : acc[i] * inv;
+            if (of != nullptr) of[d] = r;
+            else o[d] = from_f32<T>(r);
+        }
     }
 }
 

@@ -207,6 +207,7 @@ struct AttnExtra {
     int32_t keep_first;   // > 0: besides its window or chunk a query sees the keys at positions below this (at their true positions)
     int32_t gate_wide;    // > 0: `gate` holds one value per (row, q head, value) at row * gate_ld + head * value width + value
     const float* slope;   // per q head, or null: slope[h] * (i - j) is taken off the scaled score of query i and key j
+    int32_t out_f32;      // > 0: the results are written as float32 whatever the activation type (same places, counted in values)
 };
 
 // Element offset of (slot, pos, kv head, which = 0 for K / 1 for V); -1 if there is no page, or if

@@ -884,36 +884,36 @@ X0NE_API int x0ne_rope_pairs_kv_write(const void* src, int dt, int ld, int k_col
 }
 
 // ----------------------------------------------------------------------------------------
-// Differential heads.  att holds, per row, heads x 2 results of vd values (map 1, then map 2 of each head):
+// Differential heads.  att (float32) holds, per row, heads x 2 results of vd values (map 1, then map 2 of each head):
 //   o = a1 - lambda a2;  out[row][head] = o / sqrt(mean(o^2) + eps) * post * sigmoid(gate[row][head x vd + d])
 // (gate null: no gate).  One warp per (row, head); the difference, the norm and the gate are float32.
 // ----------------------------------------------------------------------------------------
 template <typename T>
-__global__ void diff_heads_kernel(const T* __restrict__ att, const T* __restrict__ gate, int64_t gate_ld, T* __restrict__ out, int n_rows,
+__global__ void diff_heads_kernel(const float* __restrict__ att, const T* __restrict__ gate, int64_t gate_ld, T* __restrict__ out, int n_rows,
                                   int heads, int vd, float lambda, float eps, float post) {
     pdl_prologue();
     const int lane = threadIdx.x & 31;
     const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= (int64_t)n_rows * heads) return;
     const int row = (int)(item / heads), head = (int)(item % heads);
-    const T* a1 = att + ((int64_t)row * heads + head) * 2 * vd;
-    const T* a2 = a1 + vd;
+    const float* a1 = att + ((int64_t)row * heads + head) * 2 * vd;
+    const float* a2 = a1 + vd;
     float ss = 0.f;
     for (int i = lane; i < vd; i += 32) {
-        const float o = to_f32(a1[i]) - lambda * to_f32(a2[i]);
+        const float o = a1[i] - lambda * a2[i];
         ss = fmaf(o, o, ss);
     }
     const float scale = post / sqrtf(warp_sum(ss) / (float)vd + eps);
     T* dst = out + ((int64_t)row * heads + head) * vd;
     const T* g = gate != nullptr ? gate + (int64_t)row * gate_ld + (int64_t)head * vd : nullptr;
     for (int i = lane; i < vd; i += 32) {
-        float o = (to_f32(a1[i]) - lambda * to_f32(a2[i])) * scale;
+        float o = (a1[i] - lambda * a2[i]) * scale;
         if (g != nullptr) o *= 1.0f / (1.0f + expf(-to_f32(g[i])));
         dst[i] = from_f32<T>(o);
     }
 }
 
-X0NE_API int x0ne_diff_heads(const void* att, const void* gate, int64_t gate_ld, void* out, int dt, int n_rows, int heads, int vd,
+X0NE_API int x0ne_diff_heads(const float* att, const void* gate, int64_t gate_ld, void* out, int dt, int n_rows, int heads, int vd,
                              float lambda, float eps, float post, cudaStream_t stream) {
     X0NE_REQUIRE(n_rows >= 0 && heads > 0 && vd > 0 && (gate == nullptr || gate_ld >= (int64_t)heads * vd), "diff_heads: rows %d heads %d of %d", n_rows, heads, vd);
     if (n_rows == 0) return 0;
@@ -921,10 +921,10 @@ X0NE_API int x0ne_diff_heads(const void* att, const void* gate, int64_t gate_ld,
     const int64_t items = (int64_t)n_rows * heads;
     const dim3 grid((unsigned)((items + warps - 1) / warps));
     if (dt == X0NE_F32)
-        x0ne_launch(diff_heads_kernel<float>, grid, dim3(warps * 32), 0, stream, (const float*)att, (const float*)gate, gate_ld, (float*)out,
+        x0ne_launch(diff_heads_kernel<float>, grid, dim3(warps * 32), 0, stream, att, (const float*)gate, gate_ld, (float*)out,
                     n_rows, heads, vd, lambda, eps, post);
     else if (dt == X0NE_BF16)
-        x0ne_launch(diff_heads_kernel<bf16>, grid, dim3(warps * 32), 0, stream, (const bf16*)att, (const bf16*)gate, gate_ld, (bf16*)out,
+        x0ne_launch(diff_heads_kernel<bf16>, grid, dim3(warps * 32), 0, stream, att, (const bf16*)gate, gate_ld, (bf16*)out,
                     n_rows, heads, vd, lambda, eps, post);
     else
         X0NE_REQUIRE(false, "diff_heads: unknown dtype tag %d", dt);

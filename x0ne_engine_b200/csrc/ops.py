@@ -47,22 +47,23 @@ class AttnExtraArg(Structure):
     """Mirror of `struct AttnExtra` in common.cuh: what an attention kernel is asked for beyond causal
     softmax over a window (all zero: nothing)."""
     _fields_ = [("chunk", c_int32), ("v_from_k", c_int32), ("sink", c_void_p), ("gate", c_void_p),
-                ("gate_ld", c_int64), ("q_ld", c_int64), ("keep_first", c_int32), ("gate_wide", c_int32), ("slope", c_void_p)]
+                ("gate_ld", c_int64), ("q_ld", c_int64), ("keep_first", c_int32), ("gate_wide", c_int32), ("slope", c_void_p), ("out_f32", c_int32)]
 
 
 def attn_extra(chunk: int = 0, v_from_k: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
                gate_ld: int = 0, q_ld: int = 0, keep_first: int = 0, gate_wide: bool = False,
-               slope: Optional[torch.Tensor] = None) -> AttnExtraArg:
+               slope: Optional[torch.Tensor] = None, out_f32: bool = False) -> AttnExtraArg:
     """`sink`: float32 per q head.  `gate`: a view whose element (row, head) lies at row * gate_ld + head; with
     `gate_wide` it holds a value per (row, head, value) at row * gate_ld + head * value width + value.
     `keep_first`: the keys at positions below it stay visible to every later query, whatever the window or chunk.
-    `slope`: float32 per q head; slope[h] * (i - j) is taken off the scaled score of query i and key j."""
+    `slope`: float32 per q head; slope[h] * (i - j) is taken off the scaled score of query i and key j.
+    `out_f32`: the results are written as float32 (the output tensor is float32) whatever the queries' type."""
     if sink is not None:
         _need(sink, torch.float32, "sink")
     if slope is not None:
         _need(slope, torch.float32, "distance slopes")
     return AttnExtraArg(int(chunk or 0), int(v_from_k or 0), _ptr(sink), _ptr(gate), int(gate_ld), int(q_ld), int(keep_first or 0),
-                        1 if gate_wide else 0, _ptr(slope))
+                        1 if gate_wide else 0, _ptr(slope), 1 if out_f32 else 0)
 
 
 class SsmArg(Structure):
@@ -527,7 +528,7 @@ def attention_rows(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheArg, row
     """The plain attention kernel: keys up to 2,048 wide, values up to 512, any window (0 = none), and
     what `extra` asks for (see `attn_extra`).  With `extra.q_ld` the queries are rows of a wider buffer."""
     lib = _lib("core")
-    _need(out, q.dtype, "attention output")
+    _need(out, torch.float32 if extra is not None and extra.out_f32 else q.dtype, "attention output")
     _need(row_slot, torch.int32, "row slots")
     _need(row_pos, torch.int32, "row positions")
     if not q.is_cuda or (extra is None or not extra.q_ld) and not q.is_contiguous():
@@ -680,7 +681,7 @@ def attention_flex_prefill(q: torch.Tensor, out: torch.Tensor, cache: PagedCache
                            seq_pos0: torch.Tensor, q_heads: int, scale: float, window: int, extra: AttnExtraArg) -> None:
     """Flash attention of a pass whose sequences bring several rows; tiles of up to 128 rows of one sequence."""
     lib = _lib("flex")
-    _need(out, torch.bfloat16, "attention output")
+    _need(out, torch.float32 if extra.out_f32 else torch.bfloat16, "attention output")
     if q.dtype != torch.bfloat16 or not q.is_cuda:
         raise KernelError("attention_flex: q is not a bfloat16 GPU tensor")
     for t, what in ((tile_seq, "tile sequences"), (tile_row0, "tile rows"), (seq_first_row, "sequence rows"),
@@ -709,7 +710,7 @@ def attention_flex_decode(q: torch.Tensor, out: torch.Tensor, cache: PagedCacheA
                           extra: AttnExtraArg, splits: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
     """One query row per sequence; `splits` blocks share a row's pages and meet in `scratch`."""
     lib = _lib("flex")
-    _need(out, torch.bfloat16, "attention output")
+    _need(out, torch.float32 if extra.out_f32 else torch.bfloat16, "attention output")
     if q.dtype != torch.bfloat16 or not q.is_cuda:
         raise KernelError("attention_flex: q is not a bfloat16 GPU tensor")
     _need(row_slot, torch.int32, "row slots")
@@ -1256,16 +1257,16 @@ def rope_pairs_kv_write(src: torch.Tensor, k_col: int, v_col: int, freq: Optiona
 def diff_heads(att: torch.Tensor, gate: Optional[torch.Tensor], gate_ld: int, out: torch.Tensor, n_rows: int, heads: int, vd: int,
                lam: float, eps: float, post: float) -> None:
     """out[row, head] = o / sqrt(mean(o^2) + eps) * post * sigmoid(gate[row, head]) with o = a1 - lam * a2, where att
-    holds [rows, heads, 2, vd] (the two maps' results of each head) and `gate` is a view whose row r starts gate_ld
-    values after row r - 1 (None: no gate)."""
+    holds float32 [rows, heads, 2, vd] (the two maps' results of each head) and `gate`, of out's type, is a view whose
+    row r starts gate_ld values after row r - 1 (None: no gate)."""
     lib = _lib("core")
-    _need(att, att.dtype, "attention maps")
-    _need(out, att.dtype, "combined heads")
+    _need(att, torch.float32, "attention maps")
+    _need(out, out.dtype, "combined heads")
     if att.shape[-1] != 2 * heads * vd or out.shape[-1] != heads * vd or att.numel() < n_rows * att.shape[-1] or out.numel() < n_rows * heads * vd:
         raise KernelError("diff_heads: shapes do not match")
-    if gate is not None and (gate.dtype != att.dtype or not gate.is_cuda):
-        raise KernelError("diff_heads: the gate is not of the maps' type")
-    _check(lib, lib.x0ne_diff_heads(_ptr(att), _ptr(gate), int(gate_ld), _ptr(out), dtype_tag(att.dtype), n_rows, heads, vd, float(lam),
+    if gate is not None and (gate.dtype != out.dtype or not gate.is_cuda):
+        raise KernelError("diff_heads: the gate is not of the output's type")
+    _check(lib, lib.x0ne_diff_heads(_ptr(att), _ptr(gate), int(gate_ld), _ptr(out), dtype_tag(out.dtype), n_rows, heads, vd, float(lam),
                                     float(eps), float(post), _stream()), "diff_heads")
 
 

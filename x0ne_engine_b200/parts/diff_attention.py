@@ -28,8 +28,9 @@ class DifferentialAttention(Mixer):
     The cache keeps a kv head's two keys as one row of 2 head_dim values beside its value.  The two maps run as
     2 q_heads query heads of the general attention kernels: a map's query is placed in its half of a row of 2 head_dim
     values with zeros in the other half, so its product with the whole key row is its product with its own key.
-    Scores, softmax, the difference, the norm and the gate are float32; lambda is worked out once at bind, in double
-    precision.
+    Scores, softmax, the maps' results (the attention kernels write them as float32: the difference of two like maps,
+    brought back to unit size, would multiply the rounding of 16-bit results), the difference, the norm and the gate
+    are float32; lambda is worked out once at bind, in double precision.
 
     Parameters: hidden_size, q_heads, kv_heads, head_dim, v_dim, scale, lambda_init, eps, position, gate,
     names.{q, k, v, g, o, lq1, lk1, lq2, lk2}.
@@ -100,7 +101,7 @@ class DifferentialAttention(Mixer):
         dt, rows, m = self.env.dtype, ctx.ws.max_rows, self.MAPS
         proj = ctx.ws.buffer("diffattn.proj", (rows, self.width), dt)
         q = ctx.ws.buffer("diffattn.q", (rows, self.q_heads * m * m * self.head_dim), dt)
-        maps = ctx.ws.buffer("diffattn.maps", (rows, self.q_heads * m * self.v_dim), dt)
+        maps = ctx.ws.buffer("diffattn.maps", (rows, self.q_heads * m * self.v_dim), torch.float32)
         att = ctx.ws.buffer("diffattn.out", (rows, self.out_dim), dt)
         out = ctx.ws.buffer("delta", (rows, self.hidden), dt)
         self.proj(x, proj, n_rows)
@@ -111,7 +112,7 @@ class DifferentialAttention(Mixer):
         table = self.position.cos_sin_table(self.env.max_positions) if rot and self.env.max_positions else None
         ops.rope_pairs_kv_write(proj, self.q_dim, self.q_dim + self.k_dim, freq, table, rot, m, self.head_dim, None, q, self.q_heads,
                                 True, view, ctx.row_slot, ctx.row_pos, n_rows)
-        run_attention_ex(ctx, q, maps, view, n_rows, self.q_heads * m, self.scale, 0, ops.attn_extra())
+        run_attention_ex(ctx, q, maps, view, n_rows, self.q_heads * m, self.scale, 0, ops.attn_extra(out_f32=True))
         gate = proj[:, self.g_col:] if self.gated else None
         ops.diff_heads(maps, gate, self.width, att, n_rows, self.q_heads, self.v_dim, self.lam, self.eps, 1.0 - self.lambda_init)
         self.o(att, out, n_rows)
