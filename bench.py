@@ -13,9 +13,9 @@ time); `e2e` is the same rate through `Model.generate` with host token lists in 
 and 64 and the milliseconds a 128-token and a 512-token prompt take through the step function; `roofline` places the decode step against the bytes it must read.  One JSON line is
 printed.  This library runs on one GPU: for --gpus above 1 a line says so and the exit code is 2.
 
-    python bench.py --design rovurax|tenetar|retuvik [--sizes 1.7b,8b] [--layers 8] [--chunk 1024] [--steps K]
+    python bench.py --design rovurax|tenetar|retuvik|barorax [--sizes 1.7b,8b] [--layers 8] [--chunk 1024] [--steps K]
 
-instead runs that design beside Qwen3 (retuvik: beside Tenetar) at equal sizes (random bfloat16 weights, the same engine,
+instead runs that design beside Qwen3 (retuvik: beside Tenetar; barorax: beside Retuvik) at equal sizes (random bfloat16 weights, the same engine,
 step function and decode graphs): one prompt of --prefill-tokens through the step function, then decode
 at --batch, device-timed; one JSON line with a row per size and design.
 """
@@ -189,6 +189,34 @@ def retuvik_config(size: dict, layers: int, vocab: int, window: int):
                              "embedding": {"scale": float(w) ** 0.5}, "layers": out, "loop": {"start": 0, "stop": layers, "times": 1}})
 
 
+def barorax_config(size: dict, layers: int, vocab: int, chunk: int):
+    """A Barorax configuration of the given layer sizes.  Of every four layers the first and third are selective
+    state-space mixers (twice the width in channels, 16 states per channel, 4 taps, a step-size rank of a sixteenth of
+    the width), the second is differential attention (half the heads, each with two maps of the head size and values
+    of twice it, rotation over half of every map) and the fourth is chunked attention with rotation, unit-norm queries
+    and keys and the sink; every layer has 16 gated experts of a sixth of the feed-forward width in 4 groups of which 2
+    stay, 4 chosen per token, and a shared expert of the same size.  The whole list is a stretch that runs once, so a
+    pass opener runs."""
+    from x0ne_engine_b200.config import config_from_dict
+    w, ff, H, G, d = size["width"], size["ff"], size["heads"], size["kv_heads"], size["dim"]
+    moe = {"kind": "moe", "expert": {"ff": ff // 6}, "shared": {"ff": ff // 6},
+           "router": {"experts": 16, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    out = []
+    for i in range(layers):
+        if i % 4 == 1:
+            layer = {"type": "attention", "mixer": {"dim": d, "heads": H // 2, "kv_heads": max(1, G // 2), "vdim": 2 * d, "scale": d ** -0.5,
+                                                    "diff": 0.3, "rot": {"base": 500000.0, "dims": d // 2}}}
+        elif i % 4 == 3:
+            layer = {"type": "attention_2", "mixer": {"dim": d, "heads": H, "kv_heads": G, "vdim": d, "scale": 8.0 / d, "mask": {"size": chunk},
+                                                      "rot": {"base": 10000.0, "dims": d}}}
+        else:
+            layer = {"type": "mamba1", "mixer": {"inner": 2 * w, "state": 16, "conv": 4, "dt_rank": w // 16}}
+        layer["mlp"] = moe
+        out.append(layer)
+    return config_from_dict({"architecture": "Barorax", "vocab": vocab, "width": w, "norm": {"eps": 1e-6}, "layers": out,
+                             "loop": {"start": 0, "stop": layers, "times": 1}})
+
+
 def design_configs(size: dict, layers: int, vocab: int, chunk: int, design: str = "rovurax"):
     """(the design's configuration, Qwen3 configuration) with the same width, heads, feed-forward, depth and
     vocabulary.  Of every four Rovurax layers three are chunk-masked attention with blended values and
@@ -203,6 +231,8 @@ def design_configs(size: dict, layers: int, vocab: int, chunk: int, design: str 
         return tenetar_config(size, layers, vocab, chunk), old
     if design == "retuvik":        # beside the closest design the library has: Tenetar (windowed attention, routed experts)
         return retuvik_config(size, layers, vocab, chunk), tenetar_config(size, layers, vocab, chunk)
+    if design == "barorax":        # beside Retuvik: a recurrent mixer with a state, attention over a bounded span, gated experts, a stretch
+        return barorax_config(size, layers, vocab, chunk), retuvik_config(size, layers, vocab, chunk)
     mlp = {"ff": ff, "kind": "dense", "limit": 7.0}
     att = {"type": "attention", "mlp": mlp, "mixer": {"dim": d, "heads": H, "kv_heads": G, "vdim": d, "scale": d ** -0.5,
                                                         "mask": {"size": chunk}, "v_mix": True}}
@@ -229,7 +259,7 @@ def design_bench(args) -> int:
     layers = args.layers or 8
     vocab = 32768
     rows_out = []
-    other = "tenetar" if args.design == "retuvik" else "qwen3"
+    other = {"retuvik": "tenetar", "barorax": "retuvik"}.get(args.design, "qwen3")
     for name in args.sizes.split(","):
         size = DESIGN_SIZES[name]
         for design, cfg in zip((args.design, other), design_configs(size, layers, vocab, args.chunk, args.design)):
@@ -303,11 +333,12 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--design", default=None, choices=["rovurax", "tenetar", "retuvik"],
-                    help="instead of the default workload: this design beside Qwen3 (retuvik: beside Tenetar) at equal sizes (prefill and decode)")
+    ap.add_argument("--design", default=None, choices=["rovurax", "tenetar", "retuvik", "barorax"],
+                    help="instead of the default workload: this design beside Qwen3 (retuvik: beside Tenetar; barorax: beside Retuvik) "
+                         "at equal sizes (prefill and decode)")
     ap.add_argument("--sizes", default="1.7b,8b", help="with --design: which of " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--chunk", type=int, default=1024,
-                    help="with --design: positions per chunk of the masked attention (rovurax) or of the sliding window (tenetar, retuvik)")
+                    help="with --design: positions per chunk of the masked attention (rovurax, barorax) or of the sliding window (tenetar, retuvik)")
     args = ap.parse_args()
     if args.design is not None and args.impl == "ours" and args.gpus == 1:
         return design_bench(args)

@@ -559,6 +559,57 @@ def cmd_kernel_bench(a) -> int:
         timed(lambda: ops.wkv_scan(r, k, v, z, w0, u, h, o, state, first, slots, B, heads, n, one_token=per == 1),
               rows * hn * (3 * 2 + 4 + 4) + 2 * B * mats * 4, 4.0 * rows * hn * n)
         return 0
+    if a.kernel in ("ssm_scan", "causal_conv"):
+        # the selective state-space mixer's own kernels: --batch sequences of --m rows each, --n channels of --head-dim
+        # states, 4 taps; every sequence goes on from its state (m 1: a decode step)
+        B, per, inner, N, taps = a.batch, a.m, a.n, a.head_dim, 4
+        rows = B * per
+        state = torch.randn(B, inner * (N + taps - 1), device=dev).mul_(0.1)
+        row_slot = torch.arange(B, dtype=torch.int32, device=dev).repeat_interleave(per).contiguous()
+        row_pos = (torch.arange(per, dtype=torch.int32, device=dev) + 7).repeat(B).contiguous()
+        xz = torch.randn(rows, 2 * inner, device=dev).bfloat16()
+        u = torch.empty(rows, inner, device=dev, dtype=torch.bfloat16)
+        w, b = torch.randn(inner, taps, device=dev) * 0.5, torch.randn(inner, device=dev) * 0.1
+        copies = 1
+        if a.kernel == "causal_conv":
+            timed(lambda: ops.causal_conv_silu(xz, w, b, state, inner * N, u, row_slot, row_pos, rows, inner), rows * inner * 2 * 2)
+            return 0
+        ops.causal_conv_silu(xz, w, b, state, inner * N, u, row_slot, row_pos, rows, inner)
+        dt_raw, bc = torch.randn(rows, inner, device=dev) - 2.0, torch.randn(rows, 2 * N, device=dev)
+        A, D, dt_bias = -torch.exp(torch.randn(inner, N, device=dev)), torch.ones(inner, device=dev), torch.zeros(inner, device=dev)
+        y = torch.empty_like(u)
+        first = (torch.arange(B + 1, dtype=torch.int32, device=dev) * per).contiguous()
+        slots = torch.arange(B, dtype=torch.int32, device=dev)
+        timed(lambda: ops.selective_scan(u, xz, inner, dt_raw, dt_bias, A, bc, 0, N, D, y, state, inner * N, taps, first, slots, B),
+              rows * inner * (2 + 2 + 4 + 2) + rows * 2 * N * 4 + 2 * B * inner * N * 4, 6.0 * rows * inner * N)
+        return 0
+    if a.kernel in ("rope_pairs", "diff_heads"):
+        # the preparation of an attention with interleaved rotary pairs (--groups maps per head; unit norm with --gated) and
+        # the combination of differential heads; --m rows
+        from .cache import SequenceCache
+        from .parts.base import CacheNeed
+        rows, qh, kvh, hd, maps = a.m, a.q_heads, a.kv_heads, a.head_dim, max(1, a.groups)
+        vd = a.v_dim or hd
+        copies = 1
+        if a.kernel == "diff_heads":
+            att = torch.randn(rows, qh * 2 * vd, device=dev)
+            gate = torch.randn(rows, qh * vd, device=dev).bfloat16()
+            out = torch.empty(rows, qh * vd, device=dev, dtype=torch.bfloat16)
+            timed(lambda: ops.diff_heads(att, gate, qh * vd, out, rows, qh, vd, 0.8, 1e-6, 0.7), rows * qh * vd * (8 + 2 + 2))
+            return 0
+        cache = SequenceCache([CacheNeed("kv", kvh, maps * hd, None, v_dim=None if vd == maps * hd else vd)], [None], rows + 64, rows + 64,
+                              torch.bfloat16, dev)
+        slot = cache.acquire(rows)
+        width = (qh + kvh) * maps * hd + kvh * vd
+        src = torch.randn(rows, width, device=dev).bfloat16()
+        q_out = torch.empty(rows, qh * maps * (maps * hd if maps > 1 else hd), device=dev, dtype=torch.bfloat16)
+        freq = torch.rand(hd // 2, device=dev)
+        slots = torch.full((rows,), slot, dtype=torch.int32, device=dev)
+        pos = torch.arange(rows, dtype=torch.int32, device=dev)
+        timed(lambda: ops.rope_pairs_kv_write(src, qh * maps * hd, (qh + kvh) * maps * hd, freq, None, hd, maps, hd, 1e-6 if a.gated else None,
+                                              q_out, qh, maps > 1, cache.kv_view(0), slots, pos, rows),
+              rows * (width * 2 * 2 + (q_out.shape[1] - qh * maps * hd) * 2))
+        return 0
     if a.kernel == "head_norm_kv":
         # per-head norms of queries and keys, query temperature, unit values, keys and values into the pages; --m rows
         from .cache import SequenceCache
