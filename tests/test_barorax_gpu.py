@@ -194,7 +194,7 @@ def test_one_token_steps_give_the_bits_of_the_scan_over_all_rows(dtype, inner, n
         yt = torch.zeros_like(u)
         ops.causal_conv_silu(pick(xz), w, b, state2, inner * n, u, i32([0, 1, 2]), i32([t] * 3), B, inner)
         ops.selective_scan(u, pick(xz), inner, pick(dt_raw), dt_bias, A, pick(bc), 3, 3 + n, D, yt, state2, inner * n, taps,
-                           i32([0, 1, 1, 2, 3]), i32([0, -1, 1, 2]), 4)
+                           i32([0, 1, 1, 2, 3]), i32([0, -1, 1, 2]), 4, one_token=True)
         y2[rows] = yt
     assert torch.equal(y2, y)
     assert torch.equal(state2[0], state[2]) and torch.equal(state2[1], state[0]) and torch.equal(state2[2], state[1])

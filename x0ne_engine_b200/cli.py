@@ -580,7 +580,7 @@ def cmd_kernel_bench(a) -> int:
         y = torch.empty_like(u)
         first = (torch.arange(B + 1, dtype=torch.int32, device=dev) * per).contiguous()
         slots = torch.arange(B, dtype=torch.int32, device=dev)
-        timed(lambda: ops.selective_scan(u, xz, inner, dt_raw, dt_bias, A, bc, 0, N, D, y, state, inner * N, taps, first, slots, B),
+        timed(lambda: ops.selective_scan(u, xz, inner, dt_raw, dt_bias, A, bc, 0, N, D, y, state, inner * N, taps, first, slots, B, one_token=per == 1),
               rows * inner * (2 + 2 + 4 + 2) + rows * 2 * N * 4 + 2 * B * inner * N * 4, 6.0 * rows * inner * N)
         return 0
     if a.kernel in ("rope_pairs", "diff_heads"):

@@ -98,7 +98,7 @@ _SIGNATURES = {
     "x0ne_rope_pairs_kv_write": [_P, _I, _I, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P, _I, _I, None, _P, _P, _I, _I, _P],
     "x0ne_diff_heads": [_P, _P, _L, _P, _I, _I, _I, _I, _F, _F, _F, _P],
     "x0ne_causal_conv_silu": [_P, _L, _I, _P, _P, _P, _L, _L, _P, _P, _P, _I, _I, _I, _P],
-    "x0ne_selective_scan": ["ssm", _I, _I, _P],
+    "x0ne_selective_scan": ["ssm", _I, _I, _I, _P],
     "x0ne_add2_group_rmsnorm": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _P],
     "x0ne_open_pass": [_P, _P, _I, _P, _I, _P, _F, _P, _I, _I, _I, _P],
     "x0ne_head_norm_kv_write": [_P, _I, _I, _I, _I, _P, _P, _F, _F, _I, _I, _P, _I, None, _P, _P, _I, _P],
@@ -1292,11 +1292,13 @@ def causal_conv_silu(xz: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Ten
 
 def selective_scan(u: torch.Tensor, xz: torch.Tensor, z_col: int, dt_raw: torch.Tensor, dt_bias: Optional[torch.Tensor], A: torch.Tensor,
                    bc: torch.Tensor, b_col: int, c_col: int, D: Optional[torch.Tensor], out: torch.Tensor, state: torch.Tensor,
-                   conv_off: int, taps: int, seq_first_row: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int) -> None:
+                   conv_off: int, taps: int, seq_first_row: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int,
+                   one_token: bool = False) -> None:
     """Per sequence and channel, token by token over the sequence's rows, from and into its state row (S [channels, N] at
     0, the convolution's last taps - 1 inputs at conv_off): dt = softplus(dt_raw + dt_bias); S = exp(dt A) S + dt u B;
     out = (S . C + D u) * silu(z).  u, xz (the convolution's input at column 0, z at z_col) and out in the activation type;
-    dt_raw, A (negative), bc (B at b_col, C at c_col), D, state float32."""
+    dt_raw, A (negative), bc (B at b_col, C at c_col), D, state float32.  `one_token`: every sequence brings one row (a decode
+    step); the same bits, from a form of the kernel without idle places."""
     lib = _lib("core")
     for t, what in ((u, "scan input"), (xz, "projection"), (out, "scan output")):
         _need(t, u.dtype, what)
@@ -1312,4 +1314,4 @@ def selective_scan(u: torch.Tensor, xz: torch.Tensor, z_col: int, dt_raw: torch.
     arg = SsmArg(_ptr(u), _ptr(xz), xz.shape[-1], int(z_col), _ptr(dt_raw), _ptr(dt_bias), _ptr(A), _ptr(bc), bc.shape[-1], int(b_col),
                  int(c_col), _ptr(D), _ptr(out), _ptr(state), state.stride(0), int(conv_off), _ptr(seq_first_row), _ptr(seq_slot),
                  int(channels), int(N), int(taps))
-    _check(lib, lib.x0ne_selective_scan(arg, dtype_tag(u.dtype), n_seqs, _stream()), "selective_scan")
+    _check(lib, lib.x0ne_selective_scan(arg, dtype_tag(u.dtype), n_seqs, 1 if one_token else 0, _stream()), "selective_scan")

@@ -238,6 +238,88 @@ template <> struct SsmMath<bf16> {
     static __device__ __forceinline__ float silu(float v) { return v * __frcp_rn(1.0f + __expf(-v)); }
 };
 
+// The last K - 1 inputs of a sequence's convolution after a pass of n_tok rows from row0: rows of the pass, and, where the
+// pass brought fewer, the kept ones moved up.  One thread per channel.
+template <typename T>
+__device__ __forceinline__ void ssm_keep_inputs(const SsmArgs& a, float* st, const T* xz, int row0, int n_tok, int c) {
+    if (a.taps <= 1) return;
+    float keep[SSM_MAX_TAPS];
+    const int kept = a.taps - 1;
+#pragma unroll
+    for (int i = 0; i < SSM_MAX_TAPS; ++i) {
+        if (i >= kept) break;
+        const int t = n_tok - kept + i;         // the token of this pass that belongs at place i (negative: an older one)
+        keep[i] = t >= 0 ? to_f32(xz[(int64_t)(row0 + t) * a.xz_ld + c]) : st[a.conv_off + (int64_t)(i + n_tok) * a.channels + c];
+    }
+#pragma unroll
+    for (int i = 0; i < SSM_MAX_TAPS; ++i) {
+        if (i >= kept) break;
+        st[a.conv_off + (int64_t)i * a.channels + c] = keep[i];
+    }
+}
+
+// A pass in which every sequence brings one row (or few): a thread reads its token's values itself, nothing is staged and
+// no thread waits for another.  The operations of a token and their order are the staged kernel's, so the bits are.
+template <typename T, int NS, int SSM_SPLIT>
+__global__ void __launch_bounds__(SSM_THREADS) selective_scan_step_kernel(SsmArgs a) {
+    constexpr int SSM_CH = SSM_THREADS / SSM_SPLIT;
+    pdl_launch_dependents();
+    const int tid = threadIdx.x;
+    const int cl = tid / SSM_SPLIT, part = tid % SSM_SPLIT;
+    const int c = blockIdx.x * SSM_CH + cl;
+    const int seq = blockIdx.y;
+    const bool live = c < a.channels;
+    float An[NS], S[NS];
+    float Dc = 0.f, dtb = 0.f;
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+        const int n = part * NS + i;
+        An[i] = live && n < a.N ? a.A[(int64_t)c * a.N + n] : 0.f;
+    }
+    if (live) {
+        Dc = a.D != nullptr ? a.D[c] : 0.f;
+        dtb = a.dt_bias != nullptr ? a.dt_bias[c] : 0.f;
+    }
+    pdl_wait();
+    const int slot = a.seq_slot[seq];
+    const int row0 = a.seq_first_row[seq], n_tok = a.seq_first_row[seq + 1] - row0;
+    if (slot < 0 || n_tok <= 0) return;
+    float* st = a.state + (int64_t)slot * a.state_stride;
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+        const int n = part * NS + i;
+        S[i] = live && n < a.N ? st[(int64_t)c * a.N + n] : 0.f;
+    }
+    const T* u = (const T*)a.u;
+    const T* xz = (const T*)a.xz;
+    T* out = (T*)a.out;
+    for (int t = 0; t < n_tok; ++t) {
+        const int64_t r = row0 + t;
+        const float dt = live ? SsmMath<T>::softplus(a.dt_raw[r * a.channels + c] + dtb) : 0.f;
+        const float uv = live ? to_f32(u[r * a.channels + c]) : 0.f;
+        const float dtu = dt * uv;
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < NS; ++i) {
+            const int n = part * NS + i;
+            const float bn = n < a.N ? a.bc[r * a.bc_ld + a.b_col + n] : 0.f, cn = n < a.N ? a.bc[r * a.bc_ld + a.c_col + n] : 0.f;
+            S[i] = fmaf(SsmMath<T>::decay(dt, An[i]), S[i], dtu * bn);
+            acc = fmaf(S[i], cn, acc);
+        }
+#pragma unroll
+        for (int w = 1; w < SSM_SPLIT; w <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
+        if (part == 0 && live)
+            out[r * a.channels + c] = from_f32<T>(fmaf(Dc, uv, acc) * SsmMath<T>::silu(to_f32(xz[r * a.xz_ld + a.z_col + c])));
+    }
+    if (!live) return;
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+        const int n = part * NS + i;
+        if (n < a.N) st[(int64_t)c * a.N + n] = S[i];
+    }
+    if (part == 0) ssm_keep_inputs<T>(a, st, xz, row0, n_tok, c);
+}
+
 template <typename T, int NS, int SSM_SPLIT, int U>
 __global__ void __launch_bounds__(SSM_THREADS) selective_scan_kernel(SsmArgs a) {
     constexpr int THREADS = SSM_THREADS;
@@ -282,9 +364,14 @@ __global__ void __launch_bounds__(SSM_THREADS) selective_scan_kernel(SsmArgs a) 
     // warp until the read came back)
     float f_dt[PER_CH], f_b[PER_N], f_c[PER_N];
     T f_u[PER_CH], f_z[PER_CH];
+    // rows of a stage that are fetched and staged: the sequence's own, and the few past its end that the last group of U
+    // tokens reaches (they are staged as steps of zero)
+    auto staged_end = [&](int t0) { return t0 + (min(n_tok - t0, SSM_TC) + U - 1) / U * U; };
     auto fetch = [&](int t0) {
+        const int t_end = staged_end(t0);
 #pragma unroll
         for (int j = 0; j < PER_CH; ++j) {
+            if (t0 + j * (THREADS / SSM_CH) >= t_end) break;        // (the same for every thread: a short pass stages what it has)
             const int t = t0 + (tid / SSM_CH) + j * (THREADS / SSM_CH);
             const bool ok = t < t0 + SSM_TC && t < n_tok && ch_st < a.channels;
             const int64_t r = row0 + (ok ? t : 0);
@@ -294,6 +381,7 @@ __global__ void __launch_bounds__(SSM_THREADS) selective_scan_kernel(SsmArgs a) 
         }
 #pragma unroll
         for (int j = 0; j < PER_N; ++j) {
+            if (t0 + j * THREADS / NP >= t_end) break;
             const int e = tid + j * THREADS;
             const int t = t0 + e / NP, n = e % NP;
             const bool ok = e < SSM_TC * NP && t < n_tok && n < a.N;
@@ -304,8 +392,10 @@ __global__ void __launch_bounds__(SSM_THREADS) selective_scan_kernel(SsmArgs a) 
     };
     fetch(0);
     for (int t0 = 0; t0 < n_tok; t0 += SSM_TC) {
+        const int t_end = staged_end(t0);
 #pragma unroll
         for (int j = 0; j < PER_CH; ++j) {
+            if (t0 + j * (THREADS / SSM_CH) >= t_end) break;        // rows past those are not read: the walk below stops there
             const int tl = (tid / SSM_CH) + j * (THREADS / SSM_CH);
             if (tl < SSM_TC) {
                 // a place past the sequence's last row gets a step of zero: it leaves the state as it is, bit for bit
@@ -316,6 +406,7 @@ __global__ void __launch_bounds__(SSM_THREADS) selective_scan_kernel(SsmArgs a) 
         }
 #pragma unroll
         for (int j = 0; j < PER_N; ++j) {
+            if (t0 + j * THREADS / NP >= t_end) break;
             const int e = tid + j * THREADS;
             if (e < SSM_TC * NP) {
                 s_b[e / NP][e % NP] = f_b[j];
@@ -369,22 +460,7 @@ __global__ void __launch_bounds__(SSM_THREADS) selective_scan_kernel(SsmArgs a) 
         const int n = part * NS + i;
         if (n < a.N) st[(int64_t)c * a.N + n] = S[i];
     }
-    if (part == 0 && a.taps > 1) {
-        // the last K - 1 inputs of the convolution: rows of this pass, and, where the pass brought fewer, the kept ones moved up
-        float keep[SSM_MAX_TAPS];
-        const int kept = a.taps - 1;
-#pragma unroll
-        for (int i = 0; i < SSM_MAX_TAPS; ++i) {
-            if (i >= kept) break;
-            const int t = n_tok - kept + i;         // the token of this pass that belongs at place i (negative: an older one)
-            keep[i] = t >= 0 ? to_f32(xz[(int64_t)(row0 + t) * a.xz_ld + c]) : st[a.conv_off + (int64_t)(i + n_tok) * a.channels + c];
-        }
-#pragma unroll
-        for (int i = 0; i < SSM_MAX_TAPS; ++i) {
-            if (i >= kept) break;
-            st[a.conv_off + (int64_t)i * a.channels + c] = keep[i];
-        }
-    }
+    if (part == 0) ssm_keep_inputs<T>(a, st, xz, row0, n_tok, c);
 }
 
 // How many threads share a channel: 4, 8 or 16 (more threads per channel are more warps to hide the latency of a token's
@@ -393,7 +469,7 @@ __global__ void __launch_bounds__(SSM_THREADS) selective_scan_kernel(SsmArgs a) 
 // A float32 run's choice depends on N alone, so that a token has the same bits in every pass; a bfloat16 run takes the
 // fewest threads per channel that still give every scheduler of the GPU a few warps.
 template <typename T>
-static int selective_scan_launch(const SsmArgs& a, int n_seqs, int sm_count, cudaStream_t stream) {
+static int selective_scan_launch(const SsmArgs& a, int n_seqs, int sm_count, int one_token, cudaStream_t stream) {
     int split = a.N > 32 ? 16 : 4;
     if (sizeof(T) == 2) {
         const int64_t want_warps = (int64_t)sm_count * 4 * 3;
@@ -401,7 +477,12 @@ static int selective_scan_launch(const SsmArgs& a, int n_seqs, int sm_count, cud
     }
     const int ns = (a.N + split - 1) / split;
     const dim3 grid((unsigned)((a.channels + SSM_THREADS / split - 1) / (SSM_THREADS / split)), (unsigned)n_seqs), block(SSM_THREADS);
-#define SSM_GO(NS, SPLIT, U) x0ne_launch(selective_scan_kernel<T, NS, SPLIT, U>, grid, block, 0, stream, a)
+    // (a pass in which every sequence brings one row takes the kernel that stages nothing)
+#define SSM_GO(NS, SPLIT, U)                                                                                   \
+    do {                                                                                                       \
+        if (one_token) x0ne_launch(selective_scan_step_kernel<T, NS, SPLIT>, grid, block, 0, stream, a);       \
+        else x0ne_launch(selective_scan_kernel<T, NS, SPLIT, U>, grid, block, 0, stream, a);                   \
+    } while (0)
     if (split == 4) {
         if (ns <= 1) SSM_GO(1, 4, 4);
         else if (ns <= 2) SSM_GO(2, 4, 4);
@@ -424,7 +505,7 @@ static int selective_scan_launch(const SsmArgs& a, int n_seqs, int sm_count, cud
     X0NE_LAUNCH_CHECK();
 }
 
-X0NE_API int x0ne_selective_scan(SsmArgs a, int dt, int n_seqs, cudaStream_t stream) {
+X0NE_API int x0ne_selective_scan(SsmArgs a, int dt, int n_seqs, int one_token, cudaStream_t stream) {
     X0NE_REQUIRE(n_seqs >= 0 && n_seqs <= 65535 && a.channels > 0 && a.N > 0 && a.N <= 128 && a.taps >= 1 && a.taps <= SSM_MAX_TAPS,
                  "selective_scan: %d sequences, %d channels of %d states (at most %d), %d taps", n_seqs, a.channels, a.N, 128, a.taps);
     X0NE_REQUIRE(a.conv_off >= (int64_t)a.channels * a.N && a.state_stride >= a.conv_off + (int64_t)(a.taps - 1) * a.channels,
@@ -439,7 +520,7 @@ X0NE_API int x0ne_selective_scan(SsmArgs a, int dt, int n_seqs, cudaStream_t str
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev >= 0 ? dev : 0) != cudaSuccess || sms <= 0) sms = 148;
         if (dev >= 0) sm_count[dev] = sms;
     }
-    if (dt == X0NE_F32) return selective_scan_launch<float>(a, n_seqs, sms, stream);
-    if (dt == X0NE_BF16) return selective_scan_launch<bf16>(a, n_seqs, sms, stream);
+    if (dt == X0NE_F32) return selective_scan_launch<float>(a, n_seqs, sms, one_token, stream);
+    if (dt == X0NE_BF16) return selective_scan_launch<bf16>(a, n_seqs, sms, one_token, stream);
     X0NE_REQUIRE(false, "selective_scan: unknown dtype tag %d", dt);
 }

@@ -92,7 +92,7 @@ class SelectiveScan(Mixer):
         self.w_bc(u, bc, n_rows)
         self.w_dt(low, dt_raw, n_rows)
         ops.selective_scan(u, xz, self.inner, dt_raw, self.dt_bias, self.A, bc, 0, self.n, self.D, y, state, self.conv_off, self.taps,
-                           ctx.seq_first_row, ctx.seq_slot, ctx.n_seqs)
+                           ctx.seq_first_row, ctx.seq_slot, ctx.n_seqs, one_token=ctx.decode)
         self.o(y, delta, n_rows)
         return delta
 
