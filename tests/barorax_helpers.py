@@ -70,9 +70,9 @@ CONFIGS = {
                                layer("attention_2", chunk_attn(scale=0.8), None), layer("mamba1", mamba(36, 10, 3, 7), moe(4, 1, 32, None, 1.0, None))],
                               loop=(1, 3, 2)),
     # widths that are multiples of 16, as served models have; the stretch starts at layer 0 and runs three times
-    "even": lambda: config([layer("attention", diff_attn(32, 4, 4, 64, (16, 500000.0), 0.2, 0.18), moe(8, 2, 64, (2, 1), 2.0, 96)),
-                            layer("mamba1", mamba(256, 16, 4, 8), moe(8, 2, 64, (2, 1), 2.0, 96)),
-                            layer("attention_2", chunk_attn(64, 4, 1, 64, (64, 10000.0), 130, 0.125), moe(8, 2, 64, (4, 2), 1.0, 128))],
+    "even": lambda: config([layer("attention", diff_attn(48, 4, 2, 96, (32, 100000.0), 0.2, 0.15), moe(8, 2, 48, (4, 2), 1.5, 80)),
+                            layer("mamba1", mamba(256, 16, 4, 8), moe(8, 2, 48, (4, 2), 1.5, 80)),
+                            layer("attention_2", chunk_attn(32, 8, 2, 32, (32, 20000.0), 130, 0.25), moe(8, 4, 32, (2, 2), 1.0, 128))],
                            loop=(0, 2, 3), vocab=256, width=128, eps=1e-6),
     # nothing a multiple of 8; one layer repeated four times; a router that takes every expert; groups of one expert
     "odd": lambda: config([layer("mamba1", mamba(27, 3, 2, 3), moe(3, 3, 50, (3, 3), 0.7, 10)),
